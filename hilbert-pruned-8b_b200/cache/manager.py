@@ -1,7 +1,7 @@
 """The cache: keys and values per plan entry, per sequence, in pages; fixed-size state beside it.
 
 Layout.  Time is cut into pages of ``PAGE_TOKENS`` (64) tokens.  Plan entries whose mixers
-have the same need (kv heads, head size, window) form a GROUP with storage of its own:
+have the same need (kv heads, head sizes, window, kept first tokens) form a GROUP with storage of its own:
 ``k, v: [entries, pages, kv_heads, PAGE_TOKENS, head_dim]`` and its own page pool.  A
 sequence holds, per group, the list of physical pages of its logical pages; a group with a
 window gives pages back as soon as no later token can see them.  The same page index is
@@ -72,17 +72,18 @@ class CacheGroup:
         self.index_of = {e: i for i, e in enumerate(entries)}
         self.pool = IndexPool(num_pages, "page")
         shape = (len(entries), num_pages, need.num_kv_heads, PAGE_TOKENS, need.head_dim)
+        v_shape = shape[:-1] + (need.value_dim,)
         self.shape = shape
         if allocate:
             # zero-filled: a page's unwritten tail is read by no kernel, but NaN garbage there
             # would still poison 0 * NaN in a tile-wide product
             self.k = torch.zeros(shape, dtype=dtype, device=device)
-            self.v = torch.zeros(shape, dtype=dtype, device=device)
+            self.v = torch.zeros(v_shape, dtype=dtype, device=device)
         else:
             self.k = self.v = None
 
     def bytes_per_token(self, element_size: int) -> int:
-        return 2 * len(self.entries) * self.need.num_kv_heads * self.need.head_dim * element_size
+        return len(self.entries) * self.need.num_kv_heads * (self.need.head_dim + self.need.value_dim) * element_size
 
 
 class CacheManager:
@@ -192,11 +193,12 @@ class CacheManager:
             # the oldest key any coming token can see
             oldest = max(0, first_new_position - w + 1)
             dead = oldest // PAGE_TOKENS
+            kept = pages_for(g.need.keep_first)      # the pages of the first tokens stay for good
             pages = seq.pages[gi]
-            gone = [p for p in pages[:dead] if p is not None]
+            gone = [p for p in pages[kept:dead] if p is not None]
             if gone:
                 g.pool.free(gone)
-                for i in range(min(dead, len(pages))):
+                for i in range(kept, min(dead, len(pages))):
                     pages[i] = None
                 seq.pages_version += 1
 
@@ -221,7 +223,8 @@ class CacheManager:
         keep = pages_for(length)
         for gi, g in enumerate(self.groups):
             w = g.need.window
-            if w is not None and any(p is None for p in seq.pages[gi][max(0, (length - w)) // PAGE_TOKENS:keep]):
+            if w is not None and (any(p is None for p in seq.pages[gi][max(0, (length - w)) // PAGE_TOKENS:keep])
+                                  or any(p is None for p in seq.pages[gi][:min(keep, pages_for(g.need.keep_first))])):
                 raise ValueError("cache: pages inside the rewound window were already given back")
         for gi, g in enumerate(self.groups):
             tail = seq.pages[gi][keep:]

@@ -55,6 +55,11 @@ def config_class_for(root: Dict[str, Any]) -> Any:
             return _BY_ARCHITECTURE[archs[0]]
         raise ConfigError(
             f"config: architecture {archs[0]} is not supported ({', '.join(sorted(_BY_ARCHITECTURE))})")
+    single = root.get("architecture")          # some checkpoints name their one architecture in a string
+    if isinstance(single, str):
+        if single in _BY_ARCHITECTURE:
+            return _BY_ARCHITECTURE[single]
+        raise ConfigError(f"config: architecture {single} is not supported ({', '.join(sorted(_BY_ARCHITECTURE))})")
     tc = root.get("text_config")
     cfg = tc if isinstance(tc, dict) else root
     mt = cfg.get("model_type")

@@ -15,14 +15,17 @@ int hb_device_info(int device, int* sm_major, int* sm_minor, int* sm_count);
 
 // `status` (here and below): the caller's int32[4] status words (common.cuh: a bounded wait that
 // ran out, non-finite logits, a bad page number, a bad token id), or null.
-// `packed`: the table is stored as contiguous 128 x 64 tiles (the layout of hb_gemm_tc's packed weights)
+// `packed`: the table is stored as contiguous 128 x 64 tiles (the layout of hb_gemm_tc's packed weights);
+// `scale` multiplies every embedding
 int hb_embed(const int* tokens, const void* table, int table_dtype, float* out, int n_tokens, int hidden,
-             int vocab, int packed, int* status, void* stream);
+             int vocab, int packed, float scale, int* status, void* stream);
 int hb_rmsnorm(const float* x, const float* weight, float eps, float offset, void* out, int out_dtype,
                const int* rows, int n_rows, int hidden, void* stream);
 int hb_silu_mul(const void* gate_up, int in_dtype, long long in_stride, void* out, int out_dtype,
                 long long out_stride, int n_rows, int inter, void* stream);
-int hb_rope_table(const int* positions, const float* inv_freq, float* out, int n_tokens, int half, void* stream);
+// out[t][i] = amplitude * (cos, sin)(inv_freq[i] * positions[t])
+int hb_rope_table(const int* positions, const float* inv_freq, float* out, int n_tokens, int half, float amplitude,
+                  void* stream);
 int hb_rope_kv_append(void* qkv, int qkv_dtype, long long qkv_stride, const float* table, int rot,
                       int n_heads, int n_kv_heads, int head_dim, void* k_cache, void* v_cache, int cache_dtype,
                       const int* page_table, int pt_width, const int* tok_seq, const int* positions,
@@ -90,6 +93,38 @@ int hb_attention_prefill_tc(const void* q, long long q_stride, long long n_token
                             const int* page_table, int pt_width, const int* seq_start, const int* seq_pos0, void* out,
                             long long out_stride, int n_seqs, int q_blocks, int n_heads, int n_kv_heads, int head_dim,
                             float scale, int window, int n_pages, int* error_flag, void* stream);
+// Dynamic tanh: out[r] = tanh(alpha[0] * x[rows[r]]) * w + b (rows null: row r)
+int hb_dyt(const float* x, const float* w, const float* b, const float* alpha, void* out, int out_dtype, long long ldo,
+           const int* rows, int n_rows, int C, void* stream);
+// Short causal convolution over time with the last taps - 1 inputs of every sequence as state
+// ([slot][taps - 1][C] floats at state + slot * state_stride): out = h + conv(h); with norm_w the
+// input is the residual stream and h = dyt(x) is made on the way.
+int hb_short_conv(const float* x, const float* norm_w, const float* norm_b, const float* norm_alpha, const float* conv_w,
+                  int taps, float* state, long long state_stride, const int* state_slots, const int* seq_start, void* out,
+                  int out_dtype, long long ldo, int n_seqs, int C, void* stream);
+int hb_relu2(const void* in, int in_dtype, long long ldi, void* out, int out_dtype, long long ldo, int n_rows, int n,
+             void* stream);
+// Biases, rotation, unit norm, cache append (keys [pages][kv][64][head_dim], values [pages][kv][64][v_dim]);
+// v_mode 0: values as they are; 1: also kept in v_first [tokens][kv * v_dim]; 2: mixed with v_first by v_lambda[0]
+int hb_qkv_prepare(const void* proj, int proj_dtype, long long ldp, const float* bias, const float* table, int rot,
+                   int n_heads, int n_kv_heads, int head_dim, int v_dim, int unit_norm, float eps, void* q_out, int q_dtype,
+                   long long ldq, void* k_cache, void* v_cache, int cache_dtype, const int* page_table, int pt_width,
+                   const int* tok_seq, const int* positions, int n_tokens, int n_pages, int append, const float* v_lambda,
+                   float* v_first, int v_mode, int* status, void* stream);
+// out [tokens][heads][all_values ? kv heads : 1][v_dim] float32
+int hb_attention_sink(const void* q, int q_dtype, long long ldq, const void* k_cache, const void* v_cache, int cache_dtype,
+                      const int* page_table, int pt_width, const int* tok_seq, const int* positions, float* out, int n_tokens,
+                      int n_heads, int n_kv_heads, int head_dim, int v_dim, float scale, int window, int keep_first,
+                      int all_values, int n_pages, int* status, void* stream);
+int hb_head_mix(const float* partial, const float* mix, void* out, int out_dtype, long long ldo, int n_tokens, int n_heads,
+                int n_kv_heads, int v_dim, int n_val, int ones, void* stream);
+// proj rows: [q heads*d | k heads*d | v heads*dv | gate heads*dv | z_i heads | z_f heads]; state per slot:
+// S [heads][d][dv], n [heads][d], m [heads]; out [tokens][heads*dv] float32
+int hb_mlstm_scan(const void* proj, int proj_dtype, long long ldp, const float* gate_bias, float cap, float q_scale, float* state,
+                  long long state_stride, const int* state_slots, const int* seq_start, float* out, int n_seqs, int n_heads,
+                  int d, int dv, void* stream);
+int hb_mlstm_output(const float* o, const void* gate, int gate_dtype, long long ldg, const float* w, float eps, void* out,
+                    int out_dtype, long long ldo, int n_tokens, int n_heads, int dv, void* stream);
 // out[i] = mean + stdev * N(0, 1): element i of the counter-based stream `base`
 int hb_random_normal(void* out, int out_dtype, long long n, unsigned long long base, float stdev, float mean,
                      void* stream);

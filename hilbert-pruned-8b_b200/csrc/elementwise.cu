@@ -12,7 +12,7 @@
 // kbt of them): a tied output head and the embedding then share ONE copy of the table.
 template <typename TW>
 __global__ void embed_kernel(const int* __restrict__ tokens, const TW* __restrict__ table, float* __restrict__ out,
-                             int hidden, int vocab, int kbt, int* status) {
+                             int hidden, int vocab, int kbt, float scale, int* status) {
     pdl_trigger();
     pdl_wait();
     const int t = blockIdx.x;
@@ -24,23 +24,23 @@ __global__ void embed_kernel(const int* __restrict__ tokens, const TW* __restric
     float* o = out + (size_t)t * hidden;
     if (kbt > 0) {
         const TW* band = table + ((size_t)(tok >> 7) * kbt * 128 + (tok & 127)) * 64;
-        for (int i = threadIdx.x; i < hidden; i += blockDim.x) o[i] = to_f32(band[(size_t)(i >> 6) * (128 * 64) + (i & 63)]);
+        for (int i = threadIdx.x; i < hidden; i += blockDim.x) o[i] = to_f32(band[(size_t)(i >> 6) * (128 * 64) + (i & 63)]) * scale;
     } else {
         const TW* row = table + (size_t)tok * hidden;
-        for (int i = threadIdx.x; i < hidden; i += blockDim.x) o[i] = to_f32(row[i]);
+        for (int i = threadIdx.x; i < hidden; i += blockDim.x) o[i] = to_f32(row[i]) * scale;
     }
 }
 
 extern "C" int hb_embed(const int* tokens, const void* table, int table_dtype, float* out, int n_tokens, int hidden,
-                        int vocab, int packed, int* status, void* stream) {
+                        int vocab, int packed, float scale, int* status, void* stream) {
     if (n_tokens == 0) return 0;
     HB_REQUIRE(n_tokens > 0 && hidden > 0 && vocab > 0, "embed: bad sizes");
     cudaStream_t s = (cudaStream_t)stream;
     const int kbt = packed ? (hidden + 63) / 64 : 0;
     if (table_dtype == HB_BF16)
-        hb_launch(embed_kernel<bf16>, dim3(n_tokens), dim3(256), 0, s, tokens, (const bf16*)table, out, hidden, vocab, kbt, status);
+        hb_launch(embed_kernel<bf16>, dim3(n_tokens), dim3(256), 0, s, tokens, (const bf16*)table, out, hidden, vocab, kbt, scale, status);
     else if (table_dtype == HB_F32)
-        hb_launch(embed_kernel<float>, dim3(n_tokens), dim3(256), 0, s, tokens, (const float*)table, out, hidden, vocab, kbt, status);
+        hb_launch(embed_kernel<float>, dim3(n_tokens), dim3(256), 0, s, tokens, (const float*)table, out, hidden, vocab, kbt, scale, status);
     else
         return hb_fail("embed: unsupported table dtype %d", table_dtype);
     return hb_check_launch("embed");
@@ -187,7 +187,7 @@ extern "C" int hb_silu_mul(const void* gate_up, int in_dtype, long long in_strid
 // out[t,i] = (cos, sin)(inv_freq[i] * float(position[t])), the angle a float32 product
 // (cpu_backend.c:88-93; cuda_backend.cu:232-236).
 __global__ void rope_table_kernel(const int* __restrict__ positions, const float* __restrict__ inv_freq,
-                                  float2* __restrict__ out, int n_tokens, int half) {
+                                  float2* __restrict__ out, int n_tokens, int half, float amplitude) {
     pdl_trigger();
     pdl_wait();
     const int idx = blockIdx.x * blockDim.x + threadIdx.x;
@@ -196,16 +196,16 @@ __global__ void rope_table_kernel(const int* __restrict__ positions, const float
     const float a = __fmul_rn(inv_freq[i], (float)positions[t]);
     float sn, cs;
     sincosf(a, &sn, &cs);
-    out[idx] = make_float2(cs, sn);
+    out[idx] = make_float2(cs * amplitude, sn * amplitude);
 }
 
 extern "C" int hb_rope_table(const int* positions, const float* inv_freq, float* out, int n_tokens, int half,
-                             void* stream) {
+                             float amplitude, void* stream) {
     if (n_tokens == 0 || half == 0) return 0;
     HB_REQUIRE(n_tokens > 0 && half > 0, "rope_table: bad sizes");
     const long long n = (long long)n_tokens * half;
     hb_launch(rope_table_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, (cudaStream_t)stream, positions, inv_freq, (float2*)out,
-                                                                                   n_tokens, half);
+                                                                                   n_tokens, half, amplitude);
     return hb_check_launch("rope_table");
 }
 

@@ -25,10 +25,23 @@ _c_int, _c_ll, _c_float, _c_ptr = ctypes.c_int, ctypes.c_longlong, ctypes.c_floa
 _SIGNATURES = {
     "hb_device_info": [_c_int, ctypes.POINTER(_c_int), ctypes.POINTER(_c_int), ctypes.POINTER(_c_int)],
     "hb_timeline_set": [_c_ptr, _c_ptr, _c_int, _c_int],
-    "hb_embed": [_c_ptr, _c_ptr, _c_int, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_ptr, _c_ptr],
+    "hb_embed": [_c_ptr, _c_ptr, _c_int, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_float, _c_ptr, _c_ptr],
     "hb_rmsnorm": [_c_ptr, _c_ptr, _c_float, _c_float, _c_ptr, _c_int, _c_ptr, _c_int, _c_int, _c_ptr],
     "hb_silu_mul": [_c_ptr, _c_int, _c_ll, _c_ptr, _c_int, _c_ll, _c_int, _c_int, _c_ptr],
-    "hb_rope_table": [_c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_ptr],
+    "hb_rope_table": [_c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_float, _c_ptr],
+    "hb_dyt": [_c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_ll, _c_ptr, _c_int, _c_int, _c_ptr],
+    "hb_short_conv": [_c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_ll, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_ll,
+                      _c_int, _c_int, _c_ptr],
+    "hb_relu2": [_c_ptr, _c_int, _c_ll, _c_ptr, _c_int, _c_ll, _c_int, _c_int, _c_ptr],
+    "hb_qkv_prepare": [_c_ptr, _c_int, _c_ll, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_ptr,
+                       _c_int, _c_ll, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_ptr,
+                       _c_ptr, _c_int, _c_ptr, _c_ptr],
+    "hb_attention_sink": [_c_ptr, _c_int, _c_ll, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int,
+                          _c_int, _c_int, _c_int, _c_float, _c_int, _c_int, _c_int, _c_int, _c_ptr, _c_ptr],
+    "hb_head_mix": [_c_ptr, _c_ptr, _c_ptr, _c_int, _c_ll, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr],
+    "hb_mlstm_scan": [_c_ptr, _c_int, _c_ll, _c_ptr, _c_float, _c_float, _c_ptr, _c_ll, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int,
+                      _c_int, _c_int, _c_ptr],
+    "hb_mlstm_output": [_c_ptr, _c_ptr, _c_int, _c_ll, _c_ptr, _c_float, _c_ptr, _c_int, _c_ll, _c_int, _c_int, _c_int, _c_ptr],
     "hb_rope_kv_append": [_c_ptr, _c_int, _c_ll, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_ptr, _c_ptr, _c_int,
                           _c_ptr, _c_int, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_ptr, _c_ptr],
     "hb_gemm_general": [_c_ptr, _c_int, _c_ll, _c_ptr, _c_int, _c_ll, _c_ptr, _c_int, _c_ll, _c_int, _c_int, _c_int,
@@ -295,8 +308,8 @@ class Ops:
                 raise KernelError(f"tensor on {t.device}, kernels bound to {self.device}")
 
     # ------------------------------------------------------------------ elementwise
-    def embed(self, tokens, table, out) -> None:
-        """``out[t] = table[tokens[t]]`` widened to 32-bit; ``table`` row-major or a PackedWeight."""
+    def embed(self, tokens, table, out, scale: float = 1.0) -> None:
+        """``out[t] = table[tokens[t]] * scale`` in 32-bit; ``table`` row-major or a PackedWeight."""
         packed = isinstance(table, PackedWeight)
         self._dev(tokens, table.data if packed else table, out)
         if tokens.dtype != torch.int32 or out.dtype != torch.float32 or not out.is_contiguous() \
@@ -306,7 +319,7 @@ class Ops:
         if table.shape[1] != H or tokens.numel() != T:
             raise KernelError("embed: shapes do not agree")
         self._call("hb_embed", tokens.data_ptr(), table.data_ptr(), _code(table), out.data_ptr(), T, H,
-                   table.shape[0], 1 if packed else 0, self.status.data_ptr(), self._stream())
+                   table.shape[0], 1 if packed else 0, float(scale), self.status.data_ptr(), self._stream())
         self.launches += 1
 
     def rmsnorm(self, x, weight, eps: float, offset: float, out, rows=None) -> None:
@@ -339,14 +352,16 @@ class Ops:
                    _code(out), _rows(out, "silu_mul output"), out.shape[0], inter, self._stream())
         self.launches += 1
 
-    def rope_table(self, positions, inv_freq, out) -> None:
+    def rope_table(self, positions, inv_freq, out, amplitude: float = 1.0) -> None:
+        """``out[t, i] = amplitude * (cos, sin)(inv_freq[i] * positions[t])``."""
         self._dev(positions, inv_freq, out)
         T, half = out.shape[0], out.shape[1]
         if positions.dtype != torch.int32 or positions.numel() != T or inv_freq.dtype != torch.float32 \
                 or inv_freq.numel() != half or out.dtype != torch.float32 or not out.is_contiguous() \
                 or out.shape[2] != 2:
             raise KernelError("rope_table: shapes or dtypes do not agree")
-        self._call("hb_rope_table", positions.data_ptr(), inv_freq.data_ptr(), out.data_ptr(), T, half, self._stream())
+        self._call("hb_rope_table", positions.data_ptr(), inv_freq.data_ptr(), out.data_ptr(), T, half, float(amplitude),
+                   self._stream())
         self.launches += 1
 
     def rope_kv_append(self, qkv, table, rot: int, heads: int, kv_heads: int, head_dim: int, cache, step,
@@ -369,6 +384,148 @@ class Ops:
                    cache.v.data_ptr(), _code(cache.k), pt.data_ptr(), pt.shape[1], step.tok_seq.data_ptr(),
                    step.positions.data_ptr(), T, 1 if append else 0, cache.k.shape[0], self.status.data_ptr(),
                    self._stream())
+        self.launches += 1
+
+    # ------------------------------------------------------------------ dynamic tanh, short convolution, squared ReLU
+    @staticmethod
+    def _f32_vec(t, n: int, what: str):
+        if t.dtype != torch.float32 or t.numel() != n or not t.is_contiguous():
+            raise KernelError(f"{what}: a contiguous float32 tensor of {n} values expected")
+        return t.data_ptr()
+
+    def dyt(self, x, weight, bias, alpha, out, rows=None) -> None:
+        """``out[r] = tanh(alpha * x[rows[r]]) * weight + bias`` (``rows`` None: every row)."""
+        self._dev(x, weight, bias, alpha, out, rows)
+        if x.dtype != torch.float32 or not x.is_contiguous():
+            raise KernelError("dyt: contiguous float32 input expected")
+        C, n = x.shape[1], out.shape[0]
+        if out.shape[1] != C or (rows is None and n != x.shape[0]) or (rows is not None and (rows.dtype != torch.int32 or rows.numel() != n)):
+            raise KernelError("dyt: shapes do not agree")
+        self._call("hb_dyt", x.data_ptr(), self._f32_vec(weight, C, "dyt weight"), self._f32_vec(bias, C, "dyt bias"),
+                   self._f32_vec(alpha, 1, "dyt alpha"), out.data_ptr(), _code(out), _rows(out, "dyt output"),
+                   rows.data_ptr() if rows is not None else None, n, C, self._stream())
+        self.launches += 1
+
+    MAX_TAPS = 8
+
+    def short_conv(self, x, conv_weight, state, step, out, norm=None) -> None:
+        """``out = h + conv(h)`` over time per channel, ``conv(h)[t] = sum_j w[:, j] h[t - taps + 1 + j]``; ``state``
+        ``[slots, (taps - 1) * C]`` float32 (a view with its own row stride) holds every sequence's last inputs and is
+        brought up to date.  ``norm = (weight, bias, alpha)``: ``x`` is the residual stream and ``h = dyt(x)``."""
+        self._dev(x, conv_weight, state, out)
+        C = x.shape[1]
+        taps = conv_weight.shape[1]
+        if x.dtype != torch.float32 or not x.is_contiguous() or tuple(out.shape) != tuple(x.shape):
+            raise KernelError("short_conv: contiguous float32 input and an output of its shape expected")
+        if tuple(conv_weight.shape) != (C, taps) or conv_weight.dtype != torch.float32 or not conv_weight.is_contiguous():
+            raise KernelError("short_conv: float32 taps [channels, taps] expected")
+        if state.dtype != torch.float32 or state.dim() != 2 or state.shape[1] != (taps - 1) * C or (taps > 1 and state.stride(1) != 1):
+            raise KernelError("short_conv: state must be float32 [slots, (taps - 1) * channels]")
+        nw = nb = na = None
+        if norm is not None:
+            nw, nb, na = (self._f32_vec(norm[0], C, "norm weight"), self._f32_vec(norm[1], C, "norm bias"),
+                          self._f32_vec(norm[2], 1, "norm alpha"))
+        self._call("hb_short_conv", x.data_ptr(), nw, nb, na, conv_weight.data_ptr(), taps, state.data_ptr(), state.stride(0),
+                   step.state_slots.data_ptr(), step.seq_start.data_ptr(), out.data_ptr(), _code(out), _rows(out, "short_conv output"),
+                   step.num_seqs, C, self._stream())
+        self.launches += 1
+
+    def relu2(self, x, out) -> None:
+        """``out = max(x, 0)^2``."""
+        self._dev(x, out)
+        if tuple(x.shape) != tuple(out.shape):
+            raise KernelError("relu2: shapes do not agree")
+        self._call("hb_relu2", x.data_ptr(), _code(x), _rows(x, "relu2 input"), out.data_ptr(), _code(out), _rows(out, "relu2 output"),
+                   x.shape[0], x.shape[1], self._stream())
+        self.launches += 1
+
+    # ------------------------------------------------------------------ attention with kept first tokens and mixed heads
+    def qkv_prepare(self, proj, bias, table, rot: int, heads: int, kv_heads: int, head_dim: int, v_dim: int, unit_norm: bool,
+                    eps: float, q_out, cache, step, append: bool, v_lambda=None, v_first=None, v_mode: int = 0) -> None:
+        """From a step's projections ``[q | k | v]``: biases added, queries and keys turned by ``table`` and (``unit_norm``)
+        divided by their root mean square per head; queries to ``q_out``, keys and values into the cache.  ``v_mode`` 1 also
+        keeps the values in ``v_first`` (float32 ``[tokens, kv_heads * v_dim]``), 2 mixes them with it:
+        ``v <- (1 - v_lambda) v + v_lambda v_first``."""
+        self._dev(proj, bias, table, q_out, cache.k, cache.v, v_lambda, v_first)
+        T = proj.shape[0]
+        width = heads * head_dim + kv_heads * (head_dim + v_dim)
+        if proj.shape[1] < width or tuple(q_out.shape) != (T, heads * head_dim):
+            raise KernelError("qkv_prepare: shapes do not agree")
+        if rot and (table is None or table.shape[0] != T or table.shape[1] != rot // 2):
+            raise KernelError("qkv_prepare: rotary table does not match the tokens")
+        if tuple(cache.k.shape[1:]) != (kv_heads, 64, head_dim) or tuple(cache.v.shape[1:]) != (kv_heads, 64, v_dim) \
+                or not cache.k.is_contiguous() or not cache.v.is_contiguous() or cache.k.dtype != cache.v.dtype:
+            raise KernelError("qkv_prepare: cache layer does not match the heads")
+        if v_first is not None and (v_first.dtype != torch.float32 or not v_first.is_contiguous() or tuple(v_first.shape) != (T, kv_heads * v_dim)):
+            raise KernelError("qkv_prepare: the first values must be contiguous float32 [tokens, kv_heads * v_dim]")
+        pt = step.page_tables[cache.group]
+        self._call("hb_qkv_prepare", proj.data_ptr(), _code(proj), _rows(proj, "projections"),
+                   self._f32_vec(bias, width, "projection bias") if bias is not None else None,
+                   table.data_ptr() if rot else None, rot, heads, kv_heads, head_dim, v_dim, 1 if unit_norm else 0, float(eps),
+                   q_out.data_ptr(), _code(q_out), _rows(q_out, "queries"), cache.k.data_ptr(), cache.v.data_ptr(), _code(cache.k),
+                   pt.data_ptr(), pt.shape[1], step.tok_seq.data_ptr(), step.positions.data_ptr(), T, cache.k.shape[0],
+                   1 if append else 0, self._f32_vec(v_lambda, 1, "value mix") if v_lambda is not None else None,
+                   v_first.data_ptr() if v_first is not None else None, int(v_mode), self.status.data_ptr(), self._stream())
+        self.launches += 1
+
+    def attention_sink(self, q, heads: int, kv_heads: int, head_dim: int, v_dim: int, cache, step, partial, scale: float,
+                       window: Optional[int], keep_first: int, all_values: bool) -> None:
+        """Causal attention where a query at position p sees key s if ``p - s < window`` or ``s < keep_first``
+        (``window`` None: every earlier key).  ``partial`` float32 ``[tokens, heads, kv_heads if all_values else 1,
+        v_dim]``: each head's softmax weights applied to the values of every key/value head, or of its own."""
+        self._dev(q, cache.k, cache.v, partial)
+        T = q.shape[0]
+        n_val = kv_heads if all_values else 1
+        if partial.dtype != torch.float32 or not partial.is_contiguous() or partial.numel() != T * heads * n_val * v_dim:
+            raise KernelError("attention_sink: partial results must be contiguous float32 [tokens, heads, value heads, v_dim]")
+        if tuple(cache.k.shape[1:]) != (kv_heads, 64, head_dim) or tuple(cache.v.shape[1:]) != (kv_heads, 64, v_dim):
+            raise KernelError("attention_sink: cache layer does not match the heads")
+        pt = step.page_tables[cache.group]
+        self._call("hb_attention_sink", q.data_ptr(), _code(q), _rows(q, "queries"), cache.k.data_ptr(), cache.v.data_ptr(),
+                   _code(cache.k), pt.data_ptr(), pt.shape[1], step.tok_seq.data_ptr(), step.positions.data_ptr(),
+                   partial.data_ptr(), T, heads, kv_heads, head_dim, v_dim, float(scale), int(window) if window else 0,
+                   int(keep_first), 1 if all_values else 0, cache.k.shape[0], self.status.data_ptr(), self._stream())
+        self.launches += 1
+
+    def head_mix(self, partial, mix, out, heads: int, kv_heads: int, v_dim: int, n_val: int, ones: int = 0) -> None:
+        """``out[t, h] = sum_g mix[h, g] partial[t, g, kv(h)]`` (``mix`` None: the head's own); ``ones`` more columns
+        (a one, then zeros) follow, through which the next product adds a bias stored as a column of its weight."""
+        self._dev(partial, mix, out)
+        T = out.shape[0]
+        if out.shape[1] != heads * v_dim + ones or partial.numel() != T * heads * n_val * v_dim:
+            raise KernelError("head_mix: shapes do not agree")
+        self._call("hb_head_mix", partial.data_ptr(), self._f32_vec(mix, heads * heads, "head mix") if mix is not None else None,
+                   out.data_ptr(), _code(out), _rows(out, "head_mix output"), T, heads, kv_heads, v_dim, n_val, ones, self._stream())
+        self.launches += 1
+
+    # ------------------------------------------------------------------ matrix memory (mLSTM)
+    def mlstm_scan(self, proj, gate_bias, cap: float, q_scale: float, state, step, out, heads: int, d: int, dv: int) -> None:
+        """The matrix memory over a step's tokens, sequence by sequence: ``proj`` float32 rows
+        ``[q | k | v | gate | z_i | z_f]``, ``state`` float32 ``[slots, heads*d*dv + heads*d + heads]`` (S, n, m),
+        ``out`` float32 ``[tokens, heads * dv]``."""
+        self._dev(proj, gate_bias, state, out)
+        T = proj.shape[0]
+        width = 2 * heads * d + 2 * heads * dv + 2 * heads
+        if proj.dtype != torch.float32 or proj.shape[1] < width or out.dtype != torch.float32 or not out.is_contiguous() \
+                or tuple(out.shape) != (T, heads * dv):
+            raise KernelError("mlstm_scan: float32 projections [tokens, 2*heads*d + 2*heads*dv + 2*heads] and float32 output expected")
+        if state.dtype != torch.float32 or state.dim() != 2 or state.shape[1] != heads * d * dv + heads * d + heads or state.stride(1) != 1:
+            raise KernelError("mlstm_scan: state must be float32 [slots, heads*d*dv + heads*d + heads]")
+        self._call("hb_mlstm_scan", proj.data_ptr(), _code(proj), _rows(proj, "projections"),
+                   self._f32_vec(gate_bias, 2 * heads, "gate bias") if gate_bias is not None else None, float(cap), float(q_scale),
+                   state.data_ptr(), state.stride(0), step.state_slots.data_ptr(), step.seq_start.data_ptr(), out.data_ptr(),
+                   step.num_seqs, heads, d, dv, self._stream())
+        self.launches += 1
+
+    def mlstm_output(self, o, gate, weight, eps: float, out, heads: int, dv: int) -> None:
+        """``out = o / rms(o per head) * weight * sigmoid(gate)``; ``gate`` a column view of the projections."""
+        self._dev(o, gate, weight, out)
+        T = o.shape[0]
+        if o.dtype != torch.float32 or not o.is_contiguous() or tuple(gate.shape) != (T, heads * dv) or tuple(out.shape) != (T, heads * dv):
+            raise KernelError("mlstm_output: shapes do not agree")
+        self._call("hb_mlstm_output", o.data_ptr(), gate.data_ptr(), _code(gate), _rows(gate, "gate"),
+                   self._f32_vec(weight, heads * dv, "mlstm norm weight"), float(eps), out.data_ptr(), _code(out),
+                   _rows(out, "mlstm output"), T, heads, dv, self._stream())
         self.launches += 1
 
     STATUS_WORDS = 4

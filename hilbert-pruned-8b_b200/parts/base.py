@@ -19,6 +19,7 @@ What a part must provide:
   32-bit ``residual`` in place.
 * feed-forwards: ``forward(h, residual, step)``, adding likewise.
 * norms: ``forward(x, out, rows=None)``.
+* token filters: ``state_need()`` and ``forward(x, out, step, state, norm=None)``.
 * position encodings: ``rotation_table(step)`` when the encoding is a rotation of pairs of
   head dimensions by position-dependent angles (the kernels then turn queries and keys
   themselves), else ``apply(q, k, step)`` which turns them in place; see ``PositionEncoding``.
@@ -52,11 +53,19 @@ class ParamSpec:
 
 @dataclass(frozen=True)
 class CacheNeed:
-    """Keys and values a mixer keeps per token: ``window`` None keeps all of them."""
+    """Keys and values a mixer keeps per token: ``window`` None keeps all of them; with a window
+    the sequence's first ``keep_first`` tokens stay visible (and stored) for good.  ``v_head_dim``:
+    the size of a value head where it differs from a key head's."""
 
     num_kv_heads: int
     head_dim: int
     window: Optional[int] = None
+    v_head_dim: Optional[int] = None
+    keep_first: int = 0
+
+    @property
+    def value_dim(self) -> int:
+        return self.head_dim if self.v_head_dim is None else self.v_head_dim
 
 
 @dataclass(frozen=True)
@@ -140,6 +149,23 @@ class FeedForward(Part):
         raise NotImplementedError
 
 
+class TokenFilter(Part):
+    """Changes what a mixer reads by looking at a few earlier tokens of the same sequence (a short
+    convolution over time).  ``state_need()``: what it keeps per sequence between steps;
+    ``forward(x, out, step, state, norm=None)`` writes ``out`` from ``x``; a filter with
+    ``fuses_norm(norm)`` true can be handed the residual stream and the norm in front of it
+    (``norm=``) and applies both in one pass."""
+
+    def state_need(self) -> Optional[StateNeed]:
+        return None
+
+    def fuses_norm(self, norm) -> bool:
+        return False
+
+    def forward(self, x, out, step, state, norm=None) -> None:
+        raise NotImplementedError
+
+
 class Norm(Part):
     out_dtype: torch.dtype
 
@@ -207,6 +233,7 @@ class Registry:
 
 
 MIXERS = Registry("mixer")
+TOKEN_FILTERS = Registry("token filter")
 FEED_FORWARDS = Registry("feed-forward")
 NORMS = Registry("norm")
 POSITION_ENCODINGS = Registry("position encoding")

@@ -12,13 +12,16 @@ from __future__ import annotations
 
 from typing import Dict, List, Optional, Tuple
 
-from .base import BLOCKS, FEED_FORWARDS, MIXERS, NORMS, CacheNeed, Registry, StateNeed
+import torch
+
+from .base import BLOCKS, FEED_FORWARDS, MIXERS, NORMS, TOKEN_FILTERS, CacheNeed, Registry, StateNeed
 
 
 class Block:
     """Base of the arrangements: builds the parts that ``ROLES`` names from the layer's spec."""
 
     ROLES: Dict[str, Registry] = {}
+    OPTIONAL: Tuple[str, ...] = ()      # roles a layer may leave empty
 
     def __init__(self, layer_spec, ctx):
         self.spec = layer_spec
@@ -27,7 +30,8 @@ class Block:
         if extra:
             raise ValueError(f"block {layer_spec.block!r} has no role for the parts {extra} of layer "
                              f"{layer_spec.prefix!r} (its roles: {', '.join(self.ROLES)})")
-        self.parts = {role: registry.build(layer_spec.part(role), ctx) for role, registry in self.ROLES.items()}
+        self.parts = {role: registry.build(layer_spec.part(role), ctx) for role, registry in self.ROLES.items()
+                      if role not in self.OPTIONAL or role in layer_spec.parts}
         self.graph_safe = all(getattr(p, "graph_safe", True) for p in self.parts.values())
 
     def named_parts(self) -> List[Tuple[str, object]]:
@@ -104,4 +108,58 @@ class PreNormBlock(Block):
         if ff_folds:
             return self.feed_forward.forward(h, x, step, prepared=prepared, prepare=prepare_next if fold else None)
         self.feed_forward.forward(h, x, step)
+        return None
+
+
+@BLOCKS.register("prenorm_filtered")
+class FilteredPreNormBlock(Block):
+    """``x += mixer(filter(norm_a(x)))``, then, if the layer has a feed-forward,
+    ``x += feed_forward(norm_b(x))``.  The filter (a short convolution over time) and the mixer may
+    both keep per-sequence state: the block asks the cache for one area per sequence and gives each
+    its share, the filter's first.  A filter that can apply the norm in front of it itself
+    (``TokenFilter.fuses_norm``) gets the residual stream and the norm: one pass instead of two."""
+
+    ROLES = {"mixer_norm": NORMS, "mixer_filter": TOKEN_FILTERS, "mixer": MIXERS, "feed_forward_norm": NORMS,
+             "feed_forward": FEED_FORWARDS}
+    OPTIONAL = ("mixer_filter", "feed_forward_norm", "feed_forward")
+
+    def __init__(self, layer_spec, ctx):
+        super().__init__(layer_spec, ctx)
+        p = self.parts
+        self.mixer_norm, self.mixer, self.filter = p["mixer_norm"], p["mixer"], p.get("mixer_filter")
+        self.feed_forward_norm, self.feed_forward = p.get("feed_forward_norm"), p.get("feed_forward")
+        if (self.feed_forward is None) != (self.feed_forward_norm is None):
+            raise ValueError(f"layer {layer_spec.prefix!r}: a feed-forward and its norm come together")
+        needs = [part.state_need() if part is not None else None for part in (self.filter, self.mixer)]
+        for need in needs:
+            if need is not None and (need.dtype != torch.float32 or len(need.shape) != 1):
+                raise ValueError(f"layer {layer_spec.prefix!r}: per-sequence state is a flat run of 32-bit values here")
+        self._state_sizes = [0 if need is None else int(need.shape[0]) for need in needs]
+        self.fuse_norm_and_filter = True        # tests switch it off to compare the two ways
+
+    def state_need(self) -> Optional[StateNeed]:
+        total = sum(self._state_sizes)
+        return StateNeed((total,), torch.float32) if total else None
+
+    def _shares(self, state):
+        """The filter's and the mixer's views of the block's state area ``[slots, total]``."""
+        n_f, n_m = self._state_sizes
+        return (state[:, :n_f] if n_f else None), (state[:, n_f:n_f + n_m] if n_m else None)
+
+    def forward(self, x, step, cache, state, append: bool):
+        ws, cap, T = self.ctx.workspace, self.ctx.max_step_tokens, step.num_tokens
+        f_state, m_state = self._shares(state) if state is not None else (None, None)
+        h = ws.buffer("block.h", (cap, x.shape[1]), self.ctx.dtype)[:T]
+        if self.filter is None:
+            self.mixer_norm.forward(x, h)
+        elif self.fuse_norm_and_filter and self.filter.fuses_norm(self.mixer_norm):
+            self.filter.forward(x, h, step, f_state, norm=self.mixer_norm)
+        else:
+            normed = ws.buffer("block.normed", (cap, x.shape[1]), torch.float32)[:T]      # the filter reads 32-bit values
+            self.mixer_norm.forward(x, normed)
+            self.filter.forward(normed, h, step, f_state)
+        self.mixer.forward(h, x, step, cache, m_state, append)
+        if self.feed_forward is not None:
+            self.feed_forward_norm.forward(x, h)
+            self.feed_forward.forward(h, x, step)
         return None

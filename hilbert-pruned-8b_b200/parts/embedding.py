@@ -1,6 +1,7 @@
 """Token embedding and output head.
 
-``x[t] = E[token[t]]`` widened to 32-bit, no scaling (cleanroom-transformer/src/cpu_backend.c:236);
+``x[t] = E[token[t]]`` widened to 32-bit, no scaling (cleanroom-transformer/src/cpu_backend.c:236)
+unless the spec gives a ``scale``;
 ``logit[v] = dot(h, W[v])`` with ``W = E`` when the embeddings are tied, else ``lm_head.weight``,
 which carries no decoder prefix (model.c:399-406).
 """
@@ -19,13 +20,15 @@ class TokenEmbedding(Part):
         super().__init__(spec, ctx)
         self.vocab = int(spec.params["vocab_size"])
         self.hidden = int(spec.params["hidden_size"])
+        self.scale = float(spec.get("scale", 1.0))            # multiplies every embedding (a tied head reads the table itself)
+        self.tensor_name = spec.get("tensor_name", "weight")
         self.weight = None
 
     def params(self) -> List[ParamSpec]:
-        return [ParamSpec("weight", (self.vocab, self.hidden))]
+        return [ParamSpec(self.tensor_name, (self.vocab, self.hidden))]
 
     def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
-        self.weight = tensors["weight"].contiguous()
+        self.weight = tensors[self.tensor_name].contiguous()
 
     def share(self, stored) -> None:
         """Reads the table from ``stored`` from now on (the same values in the layout a tied head
@@ -33,7 +36,7 @@ class TokenEmbedding(Part):
         self.weight = stored
 
     def forward(self, tokens, out) -> None:
-        self.ctx.ops.embed(tokens, self.weight, out)
+        self.ctx.ops.embed(tokens, self.weight, out, self.scale)
 
 
 @HEADS.register("lm_head")

@@ -1,4 +1,4 @@
-"""Rotary position encoding with optional llama3 frequency scaling.
+"""Rotary position encoding with optional llama3 or YaRN frequency scaling.
 
 ``inv_freq[i] = 1 / theta^(2i/rot)`` in 32-bit, then the llama3 rule per frequency: long
 wavelengths divided by ``factor``, short ones kept, the band between interpolated
@@ -6,6 +6,13 @@ wavelengths divided by ``factor``, short ones kept, the band between interpolate
 each head is rotated by ``inv_freq[i] * float(p)`` (cpu_backend.c:87-98).  The table of
 frequencies is made once on the host; cosines and sines of a step's positions are made
 once per step on the device and shared by every layer that uses the same parameters.
+
+YaRN (``yarn = {factor, original, fast, slow}``): with ``dim(t) = rot ln(original / (2 pi t)) /
+(2 ln theta)``, ``lo = max(floor(dim(fast)), 0)``, ``hi = min(ceil(dim(slow)), rot - 1)`` and
+``ramp_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1)`` the frequency of pair i is
+``f_i / factor * ramp_i + f_i (1 - ramp_i)``: fast pairs keep their frequency, slow ones are
+stretched, the band between is blended.  Cosines and sines are all multiplied by
+``0.1 ln(factor) + 1``.
 """
 from __future__ import annotations
 
@@ -40,6 +47,27 @@ def rotary_inv_freq(rotary_dim: int, theta: float, llama3=None) -> np.ndarray:
     return freq.astype(np.float32)
 
 
+def yarn_inv_freq(rotary_dim: int, theta: float, yarn) -> np.ndarray:
+    """The YaRN frequencies, evaluated in 64-bit and rounded once to 32-bit."""
+    import math
+    i = np.arange(rotary_dim // 2, dtype=np.float64)
+    f = np.power(float(theta), -2.0 * i / rotary_dim)
+    factor, orig = float(yarn["factor"]), float(yarn["original"])
+
+    def dim_of(turns: float) -> float:
+        return rotary_dim * math.log(orig / (2.0 * math.pi * turns)) / (2.0 * math.log(float(theta)))
+
+    lo = max(math.floor(dim_of(float(yarn["fast"]))), 0)
+    hi = min(math.ceil(dim_of(float(yarn["slow"]))), rotary_dim - 1)
+    ramp = np.clip((i - lo) / max(hi - lo, 0.001), 0.0, 1.0)
+    return (f / factor * ramp + f * (1.0 - ramp)).astype(np.float32)
+
+
+def yarn_amplitude(yarn) -> float:
+    import math
+    return 0.1 * math.log(float(yarn["factor"])) + 1.0
+
+
 @POSITION_ENCODINGS.register("rotary")
 class RotaryEmbedding(PositionEncoding):
     def __init__(self, spec, ctx):
@@ -48,7 +76,14 @@ class RotaryEmbedding(PositionEncoding):
         self.rotary_dim = int(spec.params["rotary_dim"])
         if self.rotary_dim % 2 or not 0 < self.rotary_dim <= self.head_dim:
             raise ValueError(f"rotary: rotary_dim {self.rotary_dim} does not fit head_dim {self.head_dim}")
-        self.inv_freq_host = rotary_inv_freq(self.rotary_dim, float(spec.params["theta"]), spec.get("llama3"))
+        yarn = spec.get("yarn")
+        if yarn is not None and spec.get("llama3") is not None:
+            raise ValueError("rotary: llama3 and yarn scaling exclude each other")
+        if yarn is not None:
+            self.inv_freq_host = yarn_inv_freq(self.rotary_dim, float(spec.params["theta"]), yarn)
+        else:
+            self.inv_freq_host = rotary_inv_freq(self.rotary_dim, float(spec.params["theta"]), spec.get("llama3"))
+        self.amplitude = yarn_amplitude(yarn) if yarn is not None else 1.0
         self._inv_freq = None
         self._key = "rope:" + repr(spec)
 
@@ -64,7 +99,7 @@ class RotaryEmbedding(PositionEncoding):
         half = self.rotary_dim // 2
         table = self.ctx.workspace.buffer(self._key, (self.ctx.max_step_tokens, half, 2), torch.float32)
         table = table[: step.num_tokens]
-        self.ctx.ops.rope_table(step.positions, self.inv_freq, table)
+        self.ctx.ops.rope_table(step.positions, self.inv_freq, table, self.amplitude)
         step.shared[self._key] = table
 
     def rotation_table(self, step):

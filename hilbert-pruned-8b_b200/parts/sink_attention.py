@@ -1,0 +1,133 @@
+"""Grouped-query attention with a sliding window that keeps the sequence's first tokens, and
+the options that go with it here: biases on the projections, queries and keys divided by their
+root mean square after the rotation, key and value heads of different sizes, softmax weights
+mixed between the heads, and values mixed with those of an earlier layer.
+
+Per token: ``q, k, v = Wq h + bq, Wk h + bk, Wv h + bv``; the position encoding turns q and k;
+``q`` and ``k`` of every head are divided by ``sqrt(mean(x^2) + eps)`` (``qk_unit_norm``); with
+``v_mix = "mix"`` the values become ``(1 - l) v + l v_first`` where ``v_first`` are the values that
+the layer with ``v_mix = "first"`` made for the same token (same ``v_mix_key``); ``k`` and the
+mixed ``v`` go to the cache.  Query at position p sees key s if ``s <= p`` and (``p - s < window``
+or ``s < keep_first``).  ``P_g`` = softmax over the visible keys of ``q_g . k * scale``; with a
+``talk`` matrix T head h uses ``sum_g T[h, g] P_g`` on the values of its own key/value head,
+which is computed as the same mix of the sums ``P_g V`` for every value head.  The output
+projection's bias rides along as one more column of its weight (the attention output carries a
+column of ones), so the product adds it on the way into the residual stream.
+"""
+from __future__ import annotations
+
+from typing import Dict, List, Optional
+
+import torch
+
+from .base import MIXERS, POSITION_ENCODINGS, CacheNeed, Mixer, ParamSpec
+
+_BIAS_PAD = 8       # columns added to the output projection: the bias and zeros up to 16 bytes of bfloat16
+
+
+@MIXERS.register("sink_attention")
+class SinkAttention(Mixer):
+    def __init__(self, spec, ctx):
+        super().__init__(spec, ctx)
+        p = spec.params
+        self.hidden = int(p["hidden_size"])
+        self.heads = int(p["num_heads"])
+        self.kv_heads = int(p["num_kv_heads"])
+        self.head_dim = int(p["head_dim"])
+        self.v_dim = int(p.get("v_head_dim") or self.head_dim)
+        self.window: Optional[int] = p.get("window")
+        self.keep_first = int(p.get("keep_first") or 0)
+        self.scale = float(p["scale"]) if p.get("scale") is not None else float(self.head_dim) ** -0.5
+        self.bias = bool(p.get("bias", False))
+        self.qk_unit_norm = bool(p.get("qk_unit_norm", False))
+        self.eps = float(p.get("eps", 1e-6))
+        self.talk = bool(p.get("talk", False))
+        self.v_mix = p.get("v_mix")                      # None | "first" | "mix"
+        if self.v_mix not in (None, "first", "mix"):
+            raise ValueError(f"attention: v_mix {self.v_mix!r} (None, 'first' or 'mix')")
+        self.v_mix_key = "v_first:" + str(p.get("v_mix_key", ""))
+        if self.heads % self.kv_heads:
+            raise ValueError("attention: heads must be a multiple of kv heads")
+        pos = p.get("position")
+        self.position = ctx.shared_part(POSITION_ENCODINGS, pos) if pos is not None else None
+        self.graph_safe = getattr(self.position, "graph_safe", True)
+        self.q_width, self.k_width, self.v_width = self.heads * self.head_dim, self.kv_heads * self.head_dim, self.kv_heads * self.v_dim
+        self.proj_width = self.q_width + self.k_width + self.v_width
+        self.proj_ld = (self.proj_width + 7) // 8 * 8
+        self.out_width = self.heads * self.v_dim
+        self.w_qkv = self.w_o = self.b_qkv = self.talk_matrix = self.v_lambda = None
+
+    def params(self) -> List[ParamSpec]:
+        W = self.hidden
+        out = [ParamSpec("q", (self.q_width, W)), ParamSpec("k", (self.k_width, W)), ParamSpec("v", (self.v_width, W)),
+               ParamSpec("o", (W, self.out_width))]
+        if self.bias:
+            out += [ParamSpec("q.b", (self.q_width,), kind="vector", init="zeros"), ParamSpec("k.b", (self.k_width,), kind="vector", init="zeros"),
+                    ParamSpec("v.b", (self.v_width,), kind="vector", init="zeros"), ParamSpec("o.b", (W,), kind="vector", init="zeros")]
+        if self.talk:
+            out.append(ParamSpec("talk", (self.heads, self.heads)))
+        if self.v_mix is not None:
+            # the layer that only provides the first values stores the scalar too and never reads it
+            out.append(ParamSpec("vmix", (), kind="vector", init="zeros", optional=self.v_mix == "first"))
+        return out
+
+    def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
+        t = tensors
+        q, k, v, o = t["q"], t["k"], t["v"], t["o"]
+        if not (q.dtype == k.dtype == v.dtype):
+            raise ValueError("attention: q, k and v projections are stored in different dtypes")
+        rows = [q, k, v]
+        if self.proj_ld > self.proj_width:
+            rows.append(torch.zeros(self.proj_ld - self.proj_width, self.hidden, dtype=q.dtype, device=q.device))
+        pack = self.ctx.ops.pack_weight
+        self.w_qkv = pack(torch.cat(rows, dim=0).contiguous())
+        if self.bias:
+            self.b_qkv = torch.cat([t["q.b"].reshape(-1), t["k.b"].reshape(-1), t["v.b"].reshape(-1)]).to(torch.float32).contiguous()
+            extra = torch.zeros(self.hidden, _BIAS_PAD, dtype=o.dtype, device=o.device)
+            extra[:, 0] = t["o.b"].reshape(-1).to(o.dtype)
+            o = torch.cat([o, extra], dim=1)
+        self.w_o = pack(o.contiguous())
+        if self.talk:
+            self.talk_matrix = t["talk"].reshape(-1).to(torch.float32).contiguous()
+        if self.v_mix == "mix":
+            self.v_lambda = t["vmix"].reshape(1).to(torch.float32).contiguous()
+
+    def weight_bytes(self) -> int:
+        return sum(w.numel() * w.element_size() for w in (self.w_qkv, self.w_o))
+
+    def cache_need(self) -> CacheNeed:
+        return CacheNeed(self.kv_heads, self.head_dim, self.window, v_head_dim=self.v_dim,
+                         keep_first=self.keep_first if self.window is not None else 0)
+
+    def forward(self, h, residual, step, cache, state, append: bool):
+        ops, ws, T, cap = self.ctx.ops, self.ctx.workspace, step.num_tokens, self.ctx.max_step_tokens
+        H, G, d, dv = self.heads, self.kv_heads, self.head_dim, self.v_dim
+        proj = ws.buffer("sink_attention.proj", (cap, self.proj_ld), torch.float32)[:T]
+        ops.linear(h, self.w_qkv, proj)
+        table, rot = None, 0
+        if self.position is not None:
+            rotation = self.position.rotation_table(step)
+            if rotation is None:
+                raise ValueError("attention: this mixer needs a position encoding that is a table of rotations")
+            table, rot = rotation
+        v_first, v_mode = None, 0
+        if self.v_mix is not None:
+            v_first = ws.buffer(self.v_mix_key, (cap, self.v_width), torch.float32)[:T]
+            if self.v_mix == "first":
+                step.shared[self.v_mix_key] = v_first
+                v_mode = 1
+            else:
+                if step.shared.get(self.v_mix_key) is None:
+                    raise ValueError("attention: values are to be mixed with those of a layer that has not run in this step")
+                v_mode = 2
+        q = ws.buffer("sink_attention.q", (cap, self.q_width), self.ctx.dtype)[:T]
+        ops.qkv_prepare(proj, self.b_qkv, table, rot, H, G, d, dv, self.qk_unit_norm, self.eps, q, cache, step, append,
+                        self.v_lambda, v_first, v_mode)
+        all_values = self.talk and G > 1
+        n_val = G if all_values else 1
+        partial = ws.buffer("sink_attention.partial", (cap, H * n_val * dv), torch.float32)[:T]
+        ops.attention_sink(q, H, G, d, dv, cache, step, partial, self.scale, self.window, self.keep_first, all_values)
+        ones = _BIAS_PAD if self.bias else 0
+        attn = ws.buffer("sink_attention.out", (cap, self.out_width + ones), self.ctx.dtype)[:T]
+        ops.head_mix(partial, self.talk_matrix, attn, H, G, dv, n_val, ones)
+        ops.linear(attn, self.w_o, residual, accumulate=True)
