@@ -146,7 +146,7 @@ class PogezenConfig:
                 rot = m["rot"]
                 position = None
                 if rot["dims"] > 0:
-                    rp: Dict[str, Any] = {"head_dim": m["dim"], "rotary_dim": rot["dims"], "theta": rot["base"]}
+                    rp: Dict[str, Any] = {"head_dim": m["dim"], "rotary_dim": rot["dims"], "theta": rot["base"], "frequencies_in_64_bit": True}
                     if rot["scaling"] is not None:
                         rp["yarn"] = dict(rot["scaling"])
                     position = PartSpec("rotary", rp)

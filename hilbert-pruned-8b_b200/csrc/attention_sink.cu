@@ -129,7 +129,7 @@ extern "C" int hb_qkv_prepare(const void* proj, int proj_dtype, long long ldp, c
 // ---------------------------------------------------------------------------------------------
 #define AS_THREADS 128
 #define AS_MAX_HD 512
-#define AS_MAX_ACC 8          // value columns per thread: (value heads served) * v_dim <= 128 * 8
+#define AS_MAX_ACC 16         // value columns per thread: (value heads served) * v_dim <= 128 * 16
 
 template <typename TQ, typename TC>
 __global__ void __launch_bounds__(AS_THREADS)

@@ -10,7 +10,7 @@
 #include "api.h"
 #include "common.cuh"
 
-#define HB_MAX_TAPS 8
+#define HB_MAX_TAPS 16
 
 template <typename TO>
 __global__ void __launch_bounds__(256)

@@ -406,7 +406,7 @@ class Ops:
                    rows.data_ptr() if rows is not None else None, n, C, self._stream())
         self.launches += 1
 
-    MAX_TAPS = 8
+    MAX_TAPS = 16
 
     def short_conv(self, x, conv_weight, state, step, out, norm=None) -> None:
         """``out = h + conv(h)`` over time per channel, ``conv(h)[t] = sum_j w[:, j] h[t - taps + 1 + j]``; ``state``

@@ -48,10 +48,13 @@ def rotary_inv_freq(rotary_dim: int, theta: float, llama3=None) -> np.ndarray:
 
 
 def yarn_inv_freq(rotary_dim: int, theta: float, yarn) -> np.ndarray:
-    """The YaRN frequencies, evaluated in 64-bit and rounded once to 32-bit."""
+    """The YaRN frequencies (``yarn`` None: the unscaled ones), evaluated in 64-bit and rounded
+    once to 32-bit."""
     import math
     i = np.arange(rotary_dim // 2, dtype=np.float64)
     f = np.power(float(theta), -2.0 * i / rotary_dim)
+    if yarn is None:
+        return f.astype(np.float32)
     factor, orig = float(yarn["factor"]), float(yarn["original"])
 
     def dim_of(turns: float) -> float:
@@ -79,7 +82,7 @@ class RotaryEmbedding(PositionEncoding):
         yarn = spec.get("yarn")
         if yarn is not None and spec.get("llama3") is not None:
             raise ValueError("rotary: llama3 and yarn scaling exclude each other")
-        if yarn is not None:
+        if yarn is not None or spec.get("frequencies_in_64_bit"):
             self.inv_freq_host = yarn_inv_freq(self.rotary_dim, float(spec.params["theta"]), yarn)
         else:
             self.inv_freq_host = rotary_inv_freq(self.rotary_dim, float(spec.params["theta"]), spec.get("llama3"))

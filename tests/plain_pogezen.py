@@ -120,13 +120,19 @@ def soft_cap(z, cap: float):
 
 
 class PlainPogezen:
-    def __init__(self, config: dict, tensors: Dict[str, torch.Tensor], dtype=torch.float64):
+    def __init__(self, config: dict, tensors: Dict[str, torch.Tensor], dtype=torch.float64, round_to=None):
+        """``round_to`` (torch.bfloat16): what a matrix product reads, and the cached keys and values,
+        are rounded to that type first, as a library that serves in it does; all else stays ``dtype``."""
         self.c = config
         self.dtype = dtype
+        self.round_to = round_to
         self.w = {n: t.to(dtype) for n, t in tensors.items()}
         self.eps = float(config["norm"]["eps"])
         self.taps = int(config["canon"]["taps"])
         self.mix_layers = [i for i, l in enumerate(config["layers"]) if l["type"] == "attention" and l["mixer"].get("v_mix")]
+
+    def r(self, x):
+        return x if self.round_to is None else x.to(self.round_to).to(self.dtype)
 
     def norm(self, x, name):
         return dyt(x, self.w[name], self.w[name + ".b"], self.w[name + ".alpha"])
@@ -141,16 +147,17 @@ class PlainPogezen:
         v = (h @ w[pre + "v"].T + w[pre + "v.b"]).view(T, G, dv)
         rot = p["rot"]
         freq, amp = yarn_frequencies(int(rot["dims"]), float(rot["base"]), rot.get("scaling"))
-        q = rms_unit(rotate(q, positions, freq, amp, int(rot["dims"])), self.eps)
-        k = rms_unit(rotate(k, positions, freq, amp, int(rot["dims"])), self.eps)
+        q = self.r(rms_unit(rotate(q, positions, freq, amp, int(rot["dims"])), self.eps))
+        k = self.r(rms_unit(rotate(k, positions, freq, amp, int(rot["dims"])), self.eps))
         if p.get("v_mix"):
             if i == self.mix_layers[0]:
                 shared["v_first"] = v
             else:
                 lam = w[pre + "vmix"]
                 v = (1.0 - lam) * v + lam * shared["v_first"]
+        v = self.r(v)
         o = talking_attention(q, k, v, w[pre + "talk"], float(p["scale"]), int(p["mask"]["size"]), int(p["mask"]["keep_first"]))
-        return o.reshape(T, H * dv) @ w[pre + "o"].T + w[pre + "o.b"]
+        return self.r(o.reshape(T, H * dv)) @ w[pre + "o"].T + w[pre + "o.b"]
 
     def mlstm(self, i: int, h):
         w, p = self.w, self.c["layers"][i]["mixer"]
@@ -164,11 +171,11 @@ class PlainPogezen:
         log_f = torch.nn.functional.logsigmoid(soft_cap(h @ w[pre + "f"].T + w[pre + "f.b"], cap))
         o = rms_unit(mlstm_scan(q, k, v, log_i, log_f), self.eps).reshape(T, H * dv)
         o = o * w[pre + "norm"] * torch.sigmoid(h @ w[pre + "g"].T)
-        return o @ w[pre + "o"].T
+        return self.r(o) @ w[pre + "o"].T
 
     def feed_forward(self, i: int, h):
         w = self.w
-        return torch.relu(h @ w[f"l{i}.mlp.up"].T) ** 2 @ w[f"l{i}.mlp.down"].T
+        return self.r(torch.relu(h @ w[f"l{i}.mlp.up"].T) ** 2) @ w[f"l{i}.mlp.down"].T
 
     def forward(self, tokens: List[int], return_layers: bool = False):
         """Logits [T, vocab] of one sequence from its first token on."""
@@ -179,10 +186,10 @@ class PlainPogezen:
         shared, layers = {}, []
         for i, layer in enumerate(self.c["layers"]):
             h = self.norm(x, f"l{i}.norm1")
-            h = h + causal_conv(h, w[f"l{i}.canon1"])
+            h = self.r(h + causal_conv(h, w[f"l{i}.canon1"]))
             x = x + (self.attention(i, h, positions, shared) if layer["type"] == "attention" else self.mlstm(i, h))
             if layer.get("mlp") is not None:
-                x = x + self.feed_forward(i, self.norm(x, f"l{i}.norm2"))
+                x = x + self.feed_forward(i, self.r(self.norm(x, f"l{i}.norm2")))
             layers.append(x)
-        logits = self.norm(x, "final.norm") @ w["embed"].T
+        logits = self.r(self.norm(x, "final.norm")) @ w["embed"].T
         return (logits, torch.stack(layers, 0)) if return_layers else logits
