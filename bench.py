@@ -3,6 +3,7 @@
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--layers L] [--impl ours|reference]
     python bench.py --workload 3b|1b      # a line of its own: unequal prompts, then decoding
     python bench.py --timeline --layers 3 --skip-points    # per-kernel times inside the decode graph
+    python bench.py --design pogezen      # a line of its own: the Pogezen design beside Llama layers of equal size
 
 Prints ONE JSON line.  A step is one decode step of a batch of 8 sequences whose caches hold
 about 8192 tokens each; ``value`` is decoded tokens per second from CUDA events around the
@@ -398,6 +399,116 @@ NO_DECODE = ("decode tokens/s: the reference generates nothing (no decode loop, 
              "through transformers and needs a tokenizer and a hub revision)")
 
 
+# --design pogezen: layer sizes that resemble real models, four layers each, random weights.  The Pogezen stack is
+# attention + feed-forward, mLSTM, attention + feed-forward, mLSTM + feed-forward; the Llama stack beside it has the
+# same width, heads, head size, feed-forward size and vocabulary.
+DESIGN_SIZES = {"2048": dict(width=2048, heads=32, kv=8, head_dim=64, ff=8192, ml_heads=8, ml_dim=64),
+                "4096": dict(width=4096, heads=32, kv=8, head_dim=128, ff=14336, ml_heads=8, ml_dim=128)}
+DESIGN_VOCAB, DESIGN_WINDOW, DESIGN_KEEP = 32000, 1024, 4
+
+
+def pogezen_config(z):
+    att = {"type": "attention", "mixer": {
+        "heads": z["heads"], "kv_heads": z["kv"], "dim": z["head_dim"], "vdim": z["head_dim"], "scale": z["head_dim"] ** -0.5,
+        "v_mix": True, "mask": {"size": DESIGN_WINDOW, "keep_first": DESIGN_KEEP},
+        "rot": {"base": 500000.0, "dims": z["head_dim"] // 2,
+                "scaling": {"factor": 8.0, "original": 8192, "fast": 32.0, "slow": 1.0}}}}
+    rec = {"type": "mlstm", "mixer": {"heads": z["ml_heads"], "dim": z["ml_dim"], "vdim": z["width"] // z["ml_heads"], "gate_cap": 15.0}}
+    mlp = {"kind": "dense", "ff": z["ff"]}
+    return {"architecture": "Pogezen", "canon": {"taps": 4}, "embedding": {"scale": 1.0}, "norm": {"eps": 1e-6},
+            "vocab": DESIGN_VOCAB, "width": z["width"],
+            "layers": [dict(att, mlp=mlp), dict(rec, mlp=None), dict(att, mlp=mlp), dict(rec, mlp=mlp)]}
+
+
+def llama_like_config(z):
+    return dict(MODEL_8B, hidden_size=z["width"], num_hidden_layers=4, intermediate_size=z["ff"], vocab_size=DESIGN_VOCAB,
+                num_attention_heads=z["heads"], num_key_value_heads=z["kv"], head_dim=z["head_dim"], tie_word_embeddings=True)
+
+
+def kernel_times(llm, run, repeats=3):
+    """Device time per library call, by name, of what ``run()`` launches (eager, CUDA events around
+    every call, the median of ``repeats`` runs): {name: [calls, microseconds]}."""
+    import torch
+    ops = llm.engine.ctx.ops
+    plain = ops._call
+    runs = []
+    for _ in range(repeats + 1):
+        marks = []
+
+        def timed(name, *args):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            plain(name, *args)
+            b.record()
+            marks.append((name, a, b))
+
+        ops._call = timed
+        try:
+            run()
+        finally:
+            ops._call = plain
+        torch.cuda.synchronize()
+        per = {}
+        for name, a, b in marks:
+            c = per.setdefault(name, [0, 0.0])
+            c[0] += 1
+            c[1] += a.elapsed_time(b) * 1e3
+        runs.append(per)
+    runs = runs[1:]
+    return {k: [runs[0][k][0], round(statistics.median(r[k][1] for r in runs), 1)] for k in runs[0]}
+
+
+def design_comparison(a) -> int:
+    import torch
+    import hilbert_pruned_8b_b200 as hb
+    from hilbert_pruned_8b_b200.api import LLM
+    from hilbert_pruned_8b_b200.engine.batch import StepEntry
+    pk, pk_src = peaks()
+    context, batch, prompt = 2048, a.batch, PREFILL_TOKENS
+    out = {}
+    for size, z in DESIGN_SIZES.items():
+        row = {}
+        for who, cfg in (("pogezen", hb.PogezenConfig.from_dict(pogezen_config(z))),
+                         ("llama", hb.LlamaConfig.from_dict(llama_like_config(z)))):
+            llm = LLM.random(cfg, seed=0, dtype="bfloat16", max_tokens=batch * (context + 128) + 2 * prompt, device=0,
+                             max_batch=batch, max_step_tokens=prompt)
+            fill_cache_random(llm)
+            eng = llm.engine
+            pms = time_prefill(llm, prompt)
+            dms, launches, step_bytes, _ = time_decode(llm, batch, a.steps, a.warmup, context)
+            toks = torch.randint(0, eng.vocab_size, (prompt,), generator=torch.Generator().manual_seed(3)).tolist()
+
+            def one_prompt():
+                s = eng.open_sequence()
+                eng.step_chunked([StepEntry(s, toks, [prompt - 1])])
+                eng.close_sequence(s)
+
+            seqs = open_filled(llm, batch, context - 64)
+            eng.use_graphs = False
+
+            def one_decode_step():
+                eng.step([StepEntry(s, [1], [0]) for s in seqs])
+
+            row[who] = {"prefill_tokens_per_s": round(prompt / (pms * 1e-3), 1), "prefill_ms": round(pms, 3),
+                        "decode_tokens_per_s": round(batch / (dms * 1e-3), 1), "decode_ms_per_step": round(dms, 4),
+                        "decode_step_gb": round(step_bytes / 1e9, 3),
+                        "decode_hbm_frac": round(step_bytes / (dms * 1e-3) / 1e9 / pk["hbm_gbs"], 4),
+                        "launches_per_decode_step": launches // max(a.steps, 1),
+                        "prefill_kernels_us": kernel_times(llm, one_prompt),
+                        "decode_kernels_us": kernel_times(llm, one_decode_step)}
+            eng.check_status()
+            del llm, eng, seqs
+            torch.cuda.empty_cache()
+        out[size] = row
+    print(json.dumps({"metric": "Pogezen layers beside Llama layers of equal size: prefill of one 2048-token prompt and decode "
+                                f"steps of batch {batch} at context {context}, four layers, random weights",
+                      "unit": "tokens/s", "dtype": "bf16", "n_gpus": 1, "steps": a.steps, "warmup": a.warmup,
+                      "config": {"window": DESIGN_WINDOW, "keep_first": DESIGN_KEEP, "vocab": DESIGN_VOCAB, "sizes": DESIGN_SIZES,
+                                 "peaks": pk_src, "hbm_gbs_peak": pk["hbm_gbs"], "bf16_tflops_peak": pk["bf16_tflops"]},
+                      "sizes": out}))
+    return 0
+
+
 def reference_arm(a) -> int:
     """The UNMODIFIED reference on the same box, for the one part of the metric it can measure: the
     warm 2048-token prefill that its own ``selftest`` command times and prints
@@ -492,6 +603,9 @@ def main() -> int:
     ap.add_argument("--skip-points", action="store_true")
     ap.add_argument("--workload", choices=("8b", "3b", "1b"), default="8b",
                     help="8b: the default line; 3b, 1b: the generation workloads at those shapes (--steps = repeats)")
+    ap.add_argument("--design", choices=("pogezen",), default=None,
+                    help="a line of its own: this design's layers beside Llama layers of equal size (prefill, decode, "
+                         "device time per kernel); the default workload is not run")
     ap.add_argument("--timeline", action="store_true",
                     help="print the per-kernel times of a decode step inside the replayed graph (builds the "
                          "timeline variant of the kernel library) instead of the JSON line")
@@ -504,6 +618,8 @@ def main() -> int:
         print(f"bench.py measures one GPU; --gpus {a.gpus} is not supported by this single-GPU library")
         return 2
     a.warmup = max(a.warmup, 3)
+    if a.design:
+        return design_comparison(a)
     if a.workload != "8b":
         return generation_workload(a.workload, repeats=min(a.steps, 3), warmup=1)
 
