@@ -101,7 +101,7 @@ int hb_dyt(const float* x, const float* w, const float* b, const float* alpha, v
 // input is the residual stream and h = dyt(x) is made on the way.
 int hb_short_conv(const float* x, const float* norm_w, const float* norm_b, const float* norm_alpha, const float* conv_w,
                   int taps, float* state, long long state_stride, const int* state_slots, const int* seq_start, void* out,
-                  int out_dtype, long long ldo, int n_seqs, int C, void* stream);
+                  int out_dtype, long long ldo, int n_seqs, int max_new, int C, void* stream);   // max_new: the most tokens a sequence brings
 int hb_relu2(const void* in, int in_dtype, long long ldi, void* out, int out_dtype, long long ldo, int n_rows, int n,
              void* stream);
 // Biases, rotation, unit norm, cache append (keys [pages][kv][64][head_dim], values [pages][kv][64][v_dim]);
@@ -118,11 +118,23 @@ int hb_attention_sink(const void* q, int q_dtype, long long ldq, const void* k_c
                       int all_values, int n_pages, int* status, void* stream);
 int hb_head_mix(const float* partial, const float* mix, void* out, int out_dtype, long long ldo, int n_tokens, int n_heads,
                 int n_kv_heads, int v_dim, int n_val, int ones, void* stream);
+// One block per (token, key split) for all heads; see attention_sink.cu.  hb_attention_heads_variant: 0 when the sizes are not built.
+int hb_attention_heads_variant(int n_heads, int n_kv_heads, int head_dim, int v_dim, int cache_dtype);
+int hb_attention_heads(const void* q, int q_dtype, long long ldq, const void* k_cache, const void* v_cache, int cache_dtype,
+                       const int* page_table, int pt_width, const int* tok_seq, const int* positions, float* partial, float* ml,
+                       const float* mix, void* out, long long ldo, int ones, int n_tokens, int n_heads, int n_kv_heads, int head_dim,
+                       int v_dim, float scale, int window, int keep_first, int splits, int n_pages, int* status, void* stream);
+int hb_head_mix_splits(const float* partial, const float* ml, const float* mix, void* out, int out_dtype, long long ldo, int n_tokens,
+                       int n_heads, int n_kv_heads, int v_dim, int splits, int ones, void* stream);
 // proj rows: [q heads*d | k heads*d | v heads*dv | gate heads*dv | z_i heads | z_f heads]; state per slot:
 // S [heads][d][dv], n [heads][d], m [heads]; out [tokens][heads*dv] float32
 int hb_mlstm_scan(const void* proj, int proj_dtype, long long ldp, const float* gate_bias, float cap, float q_scale, float* state,
                   long long state_stride, const int* state_slots, const int* seq_start, float* out, int n_seqs, int n_heads,
                   int d, int dv, void* stream);
+// the same recurrence, 32 tokens at a time (steps that bring many tokens)
+int hb_mlstm_chunks(const void* proj, int proj_dtype, long long ldp, const float* gate_bias, float cap, float q_scale, float* state,
+                    long long state_stride, const int* state_slots, const int* seq_start, float* out, int n_seqs, int n_heads,
+                    int d, int dv, void* stream);
 int hb_mlstm_output(const float* o, const void* gate, int gate_dtype, long long ldg, const float* w, float eps, void* out,
                     int out_dtype, long long ldo, int n_tokens, int n_heads, int dv, void* stream);
 // out[i] = mean + stdev * N(0, 1): element i of the counter-based stream `base`

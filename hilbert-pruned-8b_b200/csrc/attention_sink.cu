@@ -290,3 +290,345 @@ extern "C" int hb_head_mix(const float* partial, const float* mix, void* out, in
     else return hb_fail("head_mix: unsupported output dtype %d", out_dtype);
     return hb_check_launch("head_mix");
 }
+
+// ---------------------------------------------------------------------------------------------
+// attention_heads: the same attention, one block per (token, key split) for ALL query heads, so
+// that a tile of keys and values is brought into shared memory once and serves every head:
+// with mixed heads each head's weights meet the values of every key/value head, which makes
+// the weighted value sums a product [heads x keys] x [keys x (kv heads * v_dim)] per token.
+// Per tile of KT keys: scores by one thread per (kv head, key) for the heads of that group;
+// softmax bookkeeping by one warp per head (running maximum m, sum l, in float32); then every
+// thread adds the tile to its accumulators: 4 value columns for each of its heads.
+// With one split and all heads of a column in one thread the block also mixes the heads and
+// writes the attention output; otherwise it writes unnormalised sums with (m, l) per head and
+// split, and head_mix combines splits and heads.
+#define AH_THREADS 256
+#define AH_CPT 4
+
+template <typename TQ, typename TC, typename TO, int HPT, int KT>
+__global__ void __launch_bounds__(AH_THREADS)
+attention_heads_kernel(const TQ* __restrict__ q, long long ldq, const TC* __restrict__ k_cache, const TC* __restrict__ v_cache,
+                       const int* __restrict__ page_table, int pt_width, const int* __restrict__ tok_seq,
+                       const int* __restrict__ positions, float* __restrict__ partial, float* __restrict__ ml,
+                       const float* __restrict__ mix, TO* __restrict__ out, long long ldo, int ones, int nh, int nkv, int hd,
+                       int vd, float scale, int window, int keep_first, int splits, int n_pages, int* status) {
+    pdl_trigger();
+    constexpr int CE = 16 / (int)sizeof(TC);            // cache elements per 16-byte piece
+    extern __shared__ __align__(16) unsigned char ah_smem[];
+    const int NC = nkv * vd, kst = nkv * hd + CE;       // key rows are padded by 16 bytes against bank conflicts
+    float* qs = reinterpret_cast<float*>(ah_smem);      // [nh][hd]
+    float* Ss = qs + nh * hd;                           // [nh][KT]
+    float* m_s = Ss + nh * KT;                          // [nh]
+    float* l_s = m_s + nh;
+    float* c_s = l_s + nh;
+    int* key_of = reinterpret_cast<int*>(c_s + nh);     // [KT]
+    int* page_of = key_of + KT;
+    TC* Ks = reinterpret_cast<TC*>(page_of + KT + ((4 - ((nh * hd + nh * KT + 3 * nh + 2 * KT) & 3)) & 3));
+    TC* Vs = Ks + (size_t)KT * kst;
+
+    const int t = blockIdx.x, split = blockIdx.y, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int p = positions[t];
+    const int* pt = page_table + (size_t)tok_seq[t] * pt_width;
+    const int lo_w = (window > 0 && p - window + 1 > 0) ? p - window + 1 : 0;
+    const int kept = min(min(keep_first, lo_w), p + 1);
+    const int lo = max(lo_w, kept);
+    const int total = kept + (p - lo + 1);
+    const int per = (total + splits - 1) / splits;
+    const int v_begin = split * per, v_end = min(total, v_begin + per);
+    const int group = nh / nkv;
+    // this thread's value columns and heads
+    const int col_threads = (NC + AH_CPT - 1) / AH_CPT;
+    const int hg = min(AH_THREADS / col_threads, nh);
+    const int my_cg = tid % col_threads, my_hg = tid / col_threads;
+    const bool works = my_hg < hg;
+    const int col = my_cg * AH_CPT;
+    float acc[HPT][AH_CPT];
+#pragma unroll
+    for (int i = 0; i < HPT; i++)
+#pragma unroll
+        for (int j = 0; j < AH_CPT; j++) acc[i][j] = 0.0f;
+
+    pdl_wait();
+    q = pdl_fresh(q);
+    k_cache = pdl_fresh(k_cache);
+    v_cache = pdl_fresh(v_cache);
+    for (int i = tid; i < nh * hd; i += AH_THREADS) qs[i] = to_f32(q[(size_t)t * ldq + i]);
+    for (int i = tid; i < nh; i += AH_THREADS) {
+        m_s[i] = -INFINITY;
+        l_s[i] = 0.0f;
+    }
+    const int kcpr = hd / CE, vcpr = vd / CE;            // 16-byte pieces per key row and per value row
+    for (int v0 = v_begin; v0 < v_end; v0 += KT) {
+        __syncthreads();                                 // the tile before has been used up
+        if (tid < KT) {
+            const int vi = v0 + tid;
+            int s = 0, page = -1;
+            if (vi < v_end) {
+                s = vi < kept ? vi : lo + (vi - kept);
+                const int lp = s / HB_PAGE_TOKENS;
+                page = lp < pt_width ? pt[lp] : -1;
+                if (page >= n_pages) page = -1;
+                if (page < 0) hb_note(status, HB_STATUS_PAGE, 1 + tok_seq[t]);
+            }
+            key_of[tid] = s;
+            page_of[tid] = page;
+        }
+        __syncthreads();
+        // the tile's keys and values: eight 16-byte loads in flight per thread (issued before any is stored: a
+        // store to shared memory between them would keep the next load's address, read from shared memory, behind it)
+        auto copy_rows = [&](const TC* cache, TC* dst, int row_elems, int dst_stride, int cpr) {
+            const int n = KT * nkv * cpr;
+            for (int base = tid; base < n; base += AH_THREADS * 8) {
+                uint4 vals[8];
+#pragma unroll
+                for (int u = 0; u < 8; u++) {
+                    const int i = base + u * AH_THREADS;
+                    vals[u] = make_uint4(0u, 0u, 0u, 0u);
+                    if (i < n) {
+                        const int piece = i % cpr, pair = i / cpr, g = pair % nkv, r = pair / nkv;
+                        const int page = page_of[r];
+                        if (page >= 0) vals[u] = *reinterpret_cast<const uint4*>(cache + cache_offset(page, g, key_of[r], nkv, row_elems) + piece * CE);
+                    }
+                }
+#pragma unroll
+                for (int u = 0; u < 8; u++) {
+                    const int i = base + u * AH_THREADS;
+                    if (i < n) {
+                        const int piece = i % cpr, pair = i / cpr, g = pair % nkv, r = pair / nkv;
+                        *reinterpret_cast<uint4*>(dst + (size_t)r * dst_stride + g * row_elems + piece * CE) = vals[u];
+                    }
+                }
+            }
+        };
+        copy_rows(k_cache, Ks, hd, kst, kcpr);
+        copy_rows(v_cache, Vs, vd, NC, vcpr);
+        __syncthreads();
+        // scores: thread (kv head, key), the heads of the group one after the other
+        for (int i = tid; i < nkv * KT; i += AH_THREADS) {
+            const int g = i / KT, r = i - g * KT;
+            const TC* kr = Ks + (size_t)r * kst + g * hd;
+            const bool valid = v0 + r < v_end && page_of[r] >= 0;
+            for (int hh = 0; hh < group; hh++) {
+                const float* qh = qs + (g * group + hh) * hd;
+                float dot = 0.0f;
+                for (int d0 = 0; d0 < hd; d0 += CE) {
+                    const uint4 raw = *reinterpret_cast<const uint4*>(kr + d0);
+                    const TC* kv = reinterpret_cast<const TC*>(&raw);
+#pragma unroll
+                    for (int e = 0; e < CE; e++) dot = fmaf(qh[d0 + e], to_f32(kv[e]), dot);
+                }
+                Ss[(g * group + hh) * KT + r] = valid ? dot * scale : -INFINITY;
+            }
+        }
+        __syncthreads();
+        // running maximum and sum: one warp per head, one lane per key
+        for (int h = warp; h < nh; h += AH_THREADS / 32) {
+            const float s = lane < KT ? Ss[h * KT + lane] : -INFINITY;
+            const float m_old = m_s[h];
+            const float m_new = fmaxf(m_old, warp_max(s));
+            const float pr = (s == -INFINITY) ? 0.0f : expf(s - m_new);
+            const float sum = warp_sum(pr);
+            if (lane < KT) Ss[h * KT + lane] = pr;
+            if (lane == 0) {
+                const float corr = (m_old == -INFINITY) ? 0.0f : expf(m_old - m_new);
+                m_s[h] = m_new;
+                l_s[h] = l_s[h] * corr + sum;
+                c_s[h] = corr;
+            }
+        }
+        __syncthreads();
+        if (works && col < NC) {
+#pragma unroll
+            for (int i = 0; i < HPT; i++) {
+                const int h = my_hg + i * hg;
+                if (h < nh) {
+                    const float c = c_s[h];
+#pragma unroll
+                    for (int j = 0; j < AH_CPT; j++) acc[i][j] *= c;
+                }
+            }
+            const int n_keys = min(KT, v_end - v0);
+            for (int r = 0; r < n_keys; r++) {
+                float v[AH_CPT];
+                const TC* vr = Vs + (size_t)r * NC + col;
+#pragma unroll
+                for (int j = 0; j < AH_CPT; j++) v[j] = to_f32(vr[j]);
+#pragma unroll
+                for (int i = 0; i < HPT; i++) {
+                    const int h = my_hg + i * hg;
+                    if (h < nh) {
+                        const float pe = Ss[h * KT + r];
+#pragma unroll
+                        for (int j = 0; j < AH_CPT; j++) acc[i][j] = fmaf(pe, v[j], acc[i][j]);
+                    }
+                }
+            }
+        }
+    }
+    __syncthreads();
+    if (out != nullptr) {
+        // one split, every head of these columns in this thread: normalise, mix the heads, write the output
+        if (works && col < NC) {
+            const int c = col / vd, d = col - c * vd;
+            for (int h2 = c * group; h2 < (c + 1) * group; h2++) {
+                float o[AH_CPT] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+                for (int i = 0; i < HPT; i++) {
+                    if (i < nh) {
+                        const float w = (mix ? mix[h2 * nh + i] : (i == h2 ? 1.0f : 0.0f)) / l_s[i];
+#pragma unroll
+                        for (int j = 0; j < AH_CPT; j++) o[j] = fmaf(w, acc[i][j], o[j]);
+                    }
+                }
+#pragma unroll
+                for (int j = 0; j < AH_CPT; j++) out[(size_t)t * ldo + h2 * vd + d + j] = from_f32<TO>(o[j]);
+            }
+        }
+        for (int e = tid; e < ones; e += AH_THREADS) out[(size_t)t * ldo + nh * vd + e] = from_f32<TO>(e == 0 ? 1.0f : 0.0f);
+        return;
+    }
+    if (works && col < NC) {
+#pragma unroll
+        for (int i = 0; i < HPT; i++) {
+            const int h = my_hg + i * hg;
+            if (h < nh) {
+                float* o = partial + (((size_t)t * nh + h) * splits + split) * NC + col;
+                *reinterpret_cast<float4*>(o) = make_float4(acc[i][0], acc[i][1], acc[i][2], acc[i][3]);
+            }
+        }
+    }
+    for (int h = tid; h < nh; h += AH_THREADS) {
+        float* o = ml + (((size_t)t * nh + h) * splits + split) * 2;
+        o[0] = m_s[h];
+        o[1] = l_s[h];
+    }
+}
+
+static size_t ah_smem_bytes(int nh, int nkv, int hd, int vd, int kt, int cache_elem) {
+    const int ce = 16 / cache_elem;
+    size_t words = (size_t)nh * hd + (size_t)nh * kt + 3 * (size_t)nh + 2 * (size_t)kt;
+    words = (words + 3) & ~(size_t)3;
+    return words * 4 + ((size_t)kt * (nkv * hd + ce) + (size_t)kt * nkv * vd) * cache_elem;
+}
+
+// Whether attention_heads takes these sizes (else the caller uses attention_sink and head_mix):
+// returns the heads-per-thread variant (4 or 32), 0 if none fits.
+extern "C" int hb_attention_heads_variant(int n_heads, int n_kv_heads, int head_dim, int v_dim, int cache_dtype) {
+    const int elem = cache_dtype == HB_BF16 ? 2 : 4, ce = 16 / elem, kt = cache_dtype == HB_BF16 ? 32 : 16;
+    if (n_heads <= 0 || n_kv_heads <= 0 || n_heads % n_kv_heads || head_dim % ce || v_dim % ce || v_dim % AH_CPT) return 0;
+    const int nc = n_kv_heads * v_dim, col_threads = (nc + AH_CPT - 1) / AH_CPT;
+    if (col_threads > AH_THREADS) return 0;
+    if (ah_smem_bytes(n_heads, n_kv_heads, head_dim, v_dim, kt, elem) > 200 * 1024) return 0;
+    const int hg = min(AH_THREADS / col_threads, n_heads), hpt = (n_heads + hg - 1) / hg;
+    return hpt <= 4 ? 4 : hpt <= 32 ? 32 : 0;
+}
+
+template <typename TQ, typename TC, typename TO, int HPT, int KT>
+static int ah_launch(dim3 grid, size_t smem, cudaStream_t s, const void* q, long long ldq, const void* k_cache, const void* v_cache,
+                     const int* page_table, int pt_width, const int* tok_seq, const int* positions, float* partial, float* ml,
+                     const float* mix, void* out, long long ldo, int ones, int nh, int nkv, int hd, int vd, float scale, int window,
+                     int keep_first, int splits, int n_pages, int* status) {
+    static bool done[HB_MAX_DEVICES];
+    if (!done[hb_device_slot()]) {
+        cudaError_t e = cudaFuncSetAttribute(attention_heads_kernel<TQ, TC, TO, HPT, KT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        if (e != cudaSuccess) return hb_fail("attention_heads: %s", cudaGetErrorString(e));
+        done[hb_device_slot()] = true;
+    }
+    hb_launch(attention_heads_kernel<TQ, TC, TO, HPT, KT>, dim3(grid), dim3(AH_THREADS), smem, s, (const TQ*)q, ldq, (const TC*)k_cache,
+              (const TC*)v_cache, page_table, pt_width, tok_seq, positions, partial, ml, mix, (TO*)out, ldo, ones, nh, nkv, hd, vd, scale,
+              window, keep_first, splits, n_pages, status);
+    return hb_check_launch("attention_heads");
+}
+
+// out non-null (one split, the variant holds every head in one thread): the mixed, normalised output [tokens][ldo];
+// else partial [tokens][heads][splits][kv heads * v_dim] unnormalised and ml [tokens][heads][splits][2].
+extern "C" int hb_attention_heads(const void* q, int q_dtype, long long ldq, const void* k_cache, const void* v_cache, int cache_dtype,
+                                  const int* page_table, int pt_width, const int* tok_seq, const int* positions, float* partial,
+                                  float* ml, const float* mix, void* out, long long ldo, int ones, int n_tokens, int n_heads,
+                                  int n_kv_heads, int head_dim, int v_dim, float scale, int window, int keep_first, int splits,
+                                  int n_pages, int* status, void* stream) {
+    if (n_tokens == 0) return 0;
+    const int variant = hb_attention_heads_variant(n_heads, n_kv_heads, head_dim, v_dim, cache_dtype);
+    HB_REQUIRE(variant != 0, "attention_heads: these head sizes are not built");
+    HB_REQUIRE(q_dtype == cache_dtype, "attention_heads: queries and cache must have one dtype");
+    HB_REQUIRE(splits >= 1 && splits <= 65535 && window >= 0 && keep_first >= 0 && n_pages > 0, "attention_heads: bad sizes");
+    const int nc = n_kv_heads * v_dim, col_threads = (nc + AH_CPT - 1) / AH_CPT;
+    const bool whole = min(AH_THREADS / col_threads, n_heads) == 1;
+    HB_REQUIRE(out == nullptr || (splits == 1 && whole), "attention_heads: the block writes the output only with one split and every head in one thread");
+    HB_REQUIRE(out != nullptr || (partial != nullptr && ml != nullptr), "attention_heads: no place for the partial results");
+    const bool bf = cache_dtype == HB_BF16;
+    const size_t smem = ah_smem_bytes(n_heads, n_kv_heads, head_dim, v_dim, bf ? 32 : 16, bf ? 2 : 4);
+    dim3 grid(n_tokens, splits);
+    cudaStream_t s = (cudaStream_t)stream;
+#define HB_AH(TQ, TO, HPT, KT)                                                                                                     \
+    return ah_launch<TQ, TQ, TO, HPT, KT>(grid, smem, s, q, ldq, k_cache, v_cache, page_table, pt_width, tok_seq, positions, partial, ml,  \
+                                          mix, out, ldo, ones, n_heads, n_kv_heads, head_dim, v_dim, scale, window, keep_first, splits,  \
+                                          n_pages, status)
+    if (bf) { if (variant == 4) HB_AH(bf16, bf16, 4, 32); else HB_AH(bf16, bf16, 32, 32); }
+    else { if (variant == 4) HB_AH(float, float, 4, 16); else HB_AH(float, float, 32, 16); }
+#undef HB_AH
+}
+
+// Combines key splits and mixes heads: out[t, h*vd + d] = sum_g mix[h, g] * (sum_s w_gs acc[t, g, s, c(h), d]) / (sum_s w_gs l_gs),
+// w_gs = exp(m_gs - max_s m_gs); mix null: the head's own.
+template <typename TO>
+__global__ void __launch_bounds__(256)
+head_mix_splits_kernel(const float* __restrict__ partial, const float* __restrict__ ml, const float* __restrict__ mix,
+                       TO* __restrict__ out, long long ldo, int nh, int nkv, int vd, int splits, int ones) {
+    // one block per (token, value head c): first the splits of every head are combined for the columns of c
+    // (shared memory [nh][vd]), then the heads that use c mix them
+    pdl_trigger();
+    pdl_wait();
+    partial = pdl_fresh(partial);
+    ml = pdl_fresh(ml);
+    extern __shared__ float hm_smem[];
+    float* wts = hm_smem;                               // [nh][splits]: w_gs / (sum_s w_gs l_gs)
+    float* comb = hm_smem + nh * splits;                // [nh][vd]
+    const int t = blockIdx.x, c = blockIdx.y, NC = nkv * vd, group = nh / nkv;
+    for (int g = threadIdx.x; g < nh; g += blockDim.x) {
+        const float* r = ml + ((size_t)t * nh + g) * splits * 2;
+        float M = -INFINITY, den = 0.0f;
+        for (int s = 0; s < splits; s++) M = fmaxf(M, r[2 * s]);
+        for (int s = 0; s < splits; s++) den += (r[2 * s] == -INFINITY ? 0.0f : expf(r[2 * s] - M)) * r[2 * s + 1];
+        for (int s = 0; s < splits; s++) wts[g * splits + s] = den > 0.0f ? (r[2 * s] == -INFINITY ? 0.0f : expf(r[2 * s] - M)) / den : 0.0f;
+    }
+    __syncthreads();
+    const float* pr = partial + (size_t)t * nh * splits * NC + (size_t)c * vd;
+    for (int e = threadIdx.x; e < nh * vd; e += blockDim.x) {
+        const int g = e / vd, d = e - g * vd;
+        float v = 0.0f;
+        for (int s = 0; s < splits; s++) v = fmaf(wts[g * splits + s], pr[((size_t)g * splits + s) * NC + d], v);
+        comb[e] = v;
+    }
+    __syncthreads();
+    TO* o = out + (size_t)t * ldo;
+    for (int e = threadIdx.x; e < group * vd; e += blockDim.x) {
+        const int h = c * group + e / vd, d = e % vd;
+        float a;
+        if (mix != nullptr) {
+            a = 0.0f;
+            for (int g = 0; g < nh; g++) a = fmaf(mix[h * nh + g], comb[g * vd + d], a);
+        } else {
+            a = comb[h * vd + d];
+        }
+        o[h * vd + d] = from_f32<TO>(a);
+    }
+    if (c == 0)
+        for (int e = threadIdx.x; e < ones; e += blockDim.x) o[nh * vd + e] = from_f32<TO>(e == 0 ? 1.0f : 0.0f);
+}
+
+extern "C" int hb_head_mix_splits(const float* partial, const float* ml, const float* mix, void* out, int out_dtype, long long ldo,
+                                  int n_tokens, int n_heads, int n_kv_heads, int v_dim, int splits, int ones, void* stream) {
+    if (n_tokens == 0) return 0;
+    HB_REQUIRE(n_tokens > 0 && n_heads > 0 && n_kv_heads > 0 && v_dim > 0 && ones >= 0 && splits >= 1, "head_mix: bad sizes");
+    HB_REQUIRE(ldo >= (long long)n_heads * v_dim + ones, "head_mix: output rows are too short");
+    const size_t smem = ((size_t)n_heads * splits + (size_t)n_heads * v_dim) * sizeof(float);
+    HB_REQUIRE(smem <= 48 * 1024 && n_kv_heads <= 65535, "head_mix: too many heads times (splits + value size)");
+    cudaStream_t s = (cudaStream_t)stream;
+    if (out_dtype == HB_BF16)
+        hb_launch(head_mix_splits_kernel<bf16>, dim3(n_tokens, n_kv_heads), dim3(256), smem, s, partial, ml, mix, (bf16*)out, ldo, n_heads, n_kv_heads, v_dim, splits, ones);
+    else if (out_dtype == HB_F32)
+        hb_launch(head_mix_splits_kernel<float>, dim3(n_tokens, n_kv_heads), dim3(256), smem, s, partial, ml, mix, (float*)out, ldo, n_heads, n_kv_heads, v_dim, splits, ones);
+    else return hb_fail("head_mix: unsupported output dtype %d", out_dtype);
+    return hb_check_launch("head_mix_splits");
+}

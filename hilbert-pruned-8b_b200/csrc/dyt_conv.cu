@@ -38,13 +38,15 @@ extern "C" int hb_dyt(const float* x, const float* w, const float* b, const floa
     return hb_check_launch("dyt");
 }
 
-// One block per (channel chunk of 32, sequence): 32 channel lanes x 8 token lanes.  The block
-// reads the sequence's old state first, then every thread walks the sequence's tokens of this
-// step with a stride of 8, then the state is replaced by the last taps - 1 inputs (old ones
-// where the step brought fewer).  No other block touches this (sequence, channel) pair, so
-// the barrier between the reads and the writes of the state is all the ordering it needs.
+// Blocks (channel chunk of 32, sequence, run of SC_RUN tokens): 32 channel lanes x 8 token lanes.  Only
+// the block of a sequence's first run touches the state: it reads the old state first (the only tokens
+// that look back beyond the step are in its run, SC_RUN >= taps - 1), walks its tokens, and at its end
+// replaces the state by the last taps - 1 inputs of the sequence (old ones where the step brought
+// fewer), which it makes from x again.  No other block reads or writes this (sequence, channel) state,
+// so the barrier between its reads and its writes is all the ordering needed.
 #define SC_CH 32
 #define SC_TL 8
+#define SC_RUN 256
 template <typename TO, bool NORM>
 __global__ void __launch_bounds__(SC_CH * SC_TL)
 short_conv_kernel(const float* __restrict__ x, const float* __restrict__ nw, const float* __restrict__ nb,
@@ -67,12 +69,15 @@ short_conv_kernel(const float* __restrict__ x, const float* __restrict__ nw, con
         gb = live ? nb[c] : 0.0f;
     }
     const int start = seq_start[b], n = seq_start[b + 1] - start;
+    const int t_begin = blockIdx.z * SC_RUN, t_end = min(n, t_begin + SC_RUN);
+    if (t_begin >= n) return;
+    const bool first = blockIdx.z == 0;
     float* srow = state + (size_t)state_slots[b] * state_stride;
     pdl_wait();
     x = pdl_fresh(x);
     srow = pdl_fresh(srow);
 #pragma unroll
-    for (int j = 0; j < HB_MAX_TAPS - 1; j++) st[j] = (live && j < hist) ? srow[(size_t)j * C + c] : 0.0f;
+    for (int j = 0; j < HB_MAX_TAPS - 1; j++) st[j] = (first && live && j < hist) ? srow[(size_t)j * C + c] : 0.0f;
     __syncthreads();
     auto input = [&](int src) -> float {            // h of the sequence's token `src` of this step, or of an earlier step
         if (src < 0) {
@@ -85,7 +90,7 @@ short_conv_kernel(const float* __restrict__ x, const float* __restrict__ nw, con
         return NORM ? fmaf(tanhf(a * xv), gw, gb) : xv;
     };
     if (live) {
-        for (int t = tl; t < n; t += SC_TL) {
+        for (int t = t_begin + tl; t < t_end; t += SC_TL) {
             float acc = 0.0f, h = 0.0f;
 #pragma unroll
             for (int j = 0; j < HB_MAX_TAPS; j++) {
@@ -96,7 +101,7 @@ short_conv_kernel(const float* __restrict__ x, const float* __restrict__ nw, con
             }
             out[(size_t)(start + t) * ldo + c] = from_f32<TO>(h + acc);
         }
-        if (tl == 0) {
+        if (first && tl == 0) {
             for (int j = 0; j < hist; j++) srow[(size_t)j * C + c] = input(n - hist + j);
         }
     }
@@ -104,13 +109,16 @@ short_conv_kernel(const float* __restrict__ x, const float* __restrict__ nw, con
 
 extern "C" int hb_short_conv(const float* x, const float* norm_w, const float* norm_b, const float* norm_alpha,
                              const float* conv_w, int taps, float* state, long long state_stride, const int* state_slots,
-                             const int* seq_start, void* out, int out_dtype, long long ldo, int n_seqs, int C, void* stream) {
+                             const int* seq_start, void* out, int out_dtype, long long ldo, int n_seqs, int max_new, int C,
+                             void* stream) {
     if (n_seqs == 0) return 0;
-    HB_REQUIRE(n_seqs > 0 && C > 0 && ldo >= C, "short_conv: bad sizes");
+    HB_REQUIRE(n_seqs > 0 && C > 0 && ldo >= C && max_new >= 1, "short_conv: bad sizes");
+    static_assert(SC_RUN >= HB_MAX_TAPS - 1, "a sequence's first run holds every token that looks back beyond the step");
     HB_REQUIRE(taps >= 1 && taps <= HB_MAX_TAPS, "short_conv: %d taps (1..%d are built)", taps, HB_MAX_TAPS);
     HB_REQUIRE(n_seqs <= 65535, "short_conv: too many sequences");
     cudaStream_t s = (cudaStream_t)stream;
-    dim3 grid((C + SC_CH - 1) / SC_CH, n_seqs), block(SC_CH * SC_TL);
+    HB_REQUIRE((max_new + SC_RUN - 1) / SC_RUN <= 65535, "short_conv: too many tokens in one sequence's step");
+    dim3 grid((C + SC_CH - 1) / SC_CH, n_seqs, (max_new + SC_RUN - 1) / SC_RUN), block(SC_CH * SC_TL);
 #define HB_SC_LAUNCH(TO, NORM)                                                                                              \
     hb_launch(short_conv_kernel<TO, NORM>, dim3(grid), dim3(block), 0, s, x, norm_w, norm_b, norm_alpha, conv_w, taps, state,           \
               state_stride, state_slots, seq_start, (TO*)out, ldo, C)

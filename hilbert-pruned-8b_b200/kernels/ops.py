@@ -31,7 +31,7 @@ _SIGNATURES = {
     "hb_rope_table": [_c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_float, _c_ptr],
     "hb_dyt": [_c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_ll, _c_ptr, _c_int, _c_int, _c_ptr],
     "hb_short_conv": [_c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_ll, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_ll,
-                      _c_int, _c_int, _c_ptr],
+                      _c_int, _c_int, _c_int, _c_ptr],
     "hb_relu2": [_c_ptr, _c_int, _c_ll, _c_ptr, _c_int, _c_ll, _c_int, _c_int, _c_ptr],
     "hb_qkv_prepare": [_c_ptr, _c_int, _c_ll, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_ptr,
                        _c_int, _c_ll, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_ptr,
@@ -39,8 +39,13 @@ _SIGNATURES = {
     "hb_attention_sink": [_c_ptr, _c_int, _c_ll, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int,
                           _c_int, _c_int, _c_int, _c_float, _c_int, _c_int, _c_int, _c_int, _c_ptr, _c_ptr],
     "hb_head_mix": [_c_ptr, _c_ptr, _c_ptr, _c_int, _c_ll, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr],
+    "hb_attention_heads": [_c_ptr, _c_int, _c_ll, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr,
+                           _c_ll, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_int, _c_int, _c_int, _c_ptr, _c_ptr],
+    "hb_head_mix_splits": [_c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_ll, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr],
     "hb_mlstm_scan": [_c_ptr, _c_int, _c_ll, _c_ptr, _c_float, _c_float, _c_ptr, _c_ll, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int,
                       _c_int, _c_int, _c_ptr],
+    "hb_mlstm_chunks": [_c_ptr, _c_int, _c_ll, _c_ptr, _c_float, _c_float, _c_ptr, _c_ll, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int,
+                        _c_int, _c_int, _c_ptr],
     "hb_mlstm_output": [_c_ptr, _c_ptr, _c_int, _c_ll, _c_ptr, _c_float, _c_ptr, _c_int, _c_ll, _c_int, _c_int, _c_int, _c_ptr],
     "hb_rope_kv_append": [_c_ptr, _c_int, _c_ll, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_ptr, _c_ptr, _c_int,
                           _c_ptr, _c_int, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_ptr, _c_ptr],
@@ -99,6 +104,7 @@ def load_library():
         lib.hb_gemm_tc2_resident_pairs.argtypes, lib.hb_gemm_tc2_resident_pairs.restype = [_c_int], _c_int
         for name in ("hb_attention_decode_supported", "hb_attention_prefill_supported", "hb_attention_prefill_tc_supported"):
             getattr(lib, name).argtypes, getattr(lib, name).restype = [_c_int, _c_int, _c_int], _c_int
+        lib.hb_attention_heads_variant.argtypes, lib.hb_attention_heads_variant.restype = [_c_int] * 5, _c_int
         lib.hb_attention_decode_ctas_per_sm.argtypes, lib.hb_attention_decode_ctas_per_sm.restype = [_c_int], _c_int
         lib.hb_attention_decode_scratch_floats.argtypes = [_c_int, _c_int, _c_int, _c_int]
         lib.hb_attention_decode_scratch_floats.restype = _c_ll
@@ -427,7 +433,7 @@ class Ops:
                           self._f32_vec(norm[2], 1, "norm alpha"))
         self._call("hb_short_conv", x.data_ptr(), nw, nb, na, conv_weight.data_ptr(), taps, state.data_ptr(), state.stride(0),
                    step.state_slots.data_ptr(), step.seq_start.data_ptr(), out.data_ptr(), _code(out), _rows(out, "short_conv output"),
-                   step.num_seqs, C, self._stream())
+                   step.num_seqs, step.max_new, C, self._stream())
         self.launches += 1
 
     def relu2(self, x, out) -> None:
@@ -498,9 +504,69 @@ class Ops:
                    out.data_ptr(), _code(out), _rows(out, "head_mix output"), T, heads, kv_heads, v_dim, n_val, ones, self._stream())
         self.launches += 1
 
+    ATTENTION_HEADS_MAX_ROWS = 512      # tokens x key splits of a step that has fewer tokens than the device has SMs
+
+    @staticmethod
+    def attention_heads_whole(heads: int, kv_heads: int, v_dim: int) -> bool:
+        """Whether one thread of ``attention_heads`` holds every head of its value columns (the block can then mix the heads)."""
+        return min(256 // (-(-kv_heads * v_dim // 4)), heads) == 1
+
+    def attention_heads_plan(self, tokens: int, heads: int, kv_heads: int, head_dim: int, v_dim: int, dtype, longest: int):
+        """How ``attention_heads`` would run a step, or None when its kernel is not built for these sizes:
+        ``(splits, writes_output)``.  Few tokens are cut over the keys (``longest``: the most keys a token sees) so that
+        the device is busy; a step of many tokens with every head of a value column in one thread writes the mixed
+        output itself."""
+        if not self.lib.hb_attention_heads_variant(heads, kv_heads, head_dim, v_dim, _DTYPE_CODE[dtype]):
+            return None
+        whole = self.attention_heads_whole(heads, kv_heads, v_dim)
+        splits = 1
+        if tokens < self.sm_count:
+            splits = max(1, min(-(-self.sm_count // tokens), longest // 64, 32))
+        return splits, (splits == 1 and whole)
+
+    def attention_heads(self, q, heads: int, kv_heads: int, head_dim: int, v_dim: int, cache, step, scale: float, window: Optional[int],
+                        keep_first: int, splits: int, mix=None, out=None, ones: int = 0, partial=None, ml=None) -> None:
+        """The attention of ``attention_sink`` with one block per (token, key split) for all heads (each head's weights on
+        the values of every key/value head).  With ``out`` (one split): the normalised, head-mixed output and ``ones``
+        more columns (a one, then zeros).  Else ``partial`` float32 ``[tokens, heads, splits, kv_heads * v_dim]``
+        unnormalised and ``ml`` ``[tokens, heads, splits, 2]`` (maximum, sum) for ``head_mix_splits``."""
+        self._dev(q, cache.k, cache.v, out, partial, ml, mix)
+        T = q.shape[0]
+        if tuple(cache.k.shape[1:]) != (kv_heads, 64, head_dim) or tuple(cache.v.shape[1:]) != (kv_heads, 64, v_dim):
+            raise KernelError("attention_heads: cache layer does not match the heads")
+        if out is not None and (out.shape[0] != T or out.shape[1] != heads * v_dim + ones):
+            raise KernelError("attention_heads: output shape does not match")
+        if out is None and (partial is None or ml is None or partial.dtype != torch.float32 or ml.dtype != torch.float32
+                            or partial.numel() < T * heads * splits * kv_heads * v_dim or ml.numel() < T * heads * splits * 2):
+            raise KernelError("attention_heads: partial results need float32 [tokens, heads, splits, kv_heads * v_dim] and [.., 2]")
+        pt = step.page_tables[cache.group]
+        self._call("hb_attention_heads", q.data_ptr(), _code(q), _rows(q, "queries"), cache.k.data_ptr(), cache.v.data_ptr(),
+                   _code(cache.k), pt.data_ptr(), pt.shape[1], step.tok_seq.data_ptr(), step.positions.data_ptr(),
+                   partial.data_ptr() if partial is not None else None, ml.data_ptr() if ml is not None else None,
+                   self._f32_vec(mix, heads * heads, "head mix") if mix is not None else None,
+                   out.data_ptr() if out is not None else None, _rows(out, "attention output") if out is not None else 0, ones,
+                   T, heads, kv_heads, head_dim, v_dim, float(scale), int(window) if window else 0, int(keep_first), int(splits),
+                   cache.k.shape[0], self.status.data_ptr(), self._stream())
+        self.launches += 1
+
+    def head_mix_splits(self, partial, ml, mix, out, heads: int, kv_heads: int, v_dim: int, splits: int, ones: int = 0) -> None:
+        """Combines the key splits of ``attention_heads`` and mixes the heads (``mix`` None: each head its own)."""
+        self._dev(partial, ml, mix, out)
+        T = out.shape[0]
+        if out.shape[1] != heads * v_dim + ones:
+            raise KernelError("head_mix_splits: shapes do not agree")
+        self._call("hb_head_mix_splits", partial.data_ptr(), ml.data_ptr(),
+                   self._f32_vec(mix, heads * heads, "head mix") if mix is not None else None, out.data_ptr(), _code(out),
+                   _rows(out, "head_mix output"), T, heads, kv_heads, v_dim, splits, ones, self._stream())
+        self.launches += 1
+
     # ------------------------------------------------------------------ matrix memory (mLSTM)
-    def mlstm_scan(self, proj, gate_bias, cap: float, q_scale: float, state, step, out, heads: int, d: int, dv: int) -> None:
-        """The matrix memory over a step's tokens, sequence by sequence: ``proj`` float32 rows
+    MLSTM_CHUNK_FROM = 8           # steps whose longest portion has at least so many tokens run the chunked kernel
+
+    def mlstm_scan(self, proj, gate_bias, cap: float, q_scale: float, state, step, out, heads: int, d: int, dv: int,
+                   chunked: Optional[bool] = None) -> None:
+        """The matrix memory over a step's tokens, sequence by sequence (token by token, or with ``chunked``, default for
+        steps that bring ``MLSTM_CHUNK_FROM`` tokens or more to a sequence, 32 tokens at a time): ``proj`` float32 rows
         ``[q | k | v | gate | z_i | z_f]``, ``state`` float32 ``[slots, heads*d*dv + heads*d + heads]`` (S, n, m),
         ``out`` float32 ``[tokens, heads * dv]``."""
         self._dev(proj, gate_bias, state, out)
@@ -511,7 +577,9 @@ class Ops:
             raise KernelError("mlstm_scan: float32 projections [tokens, 2*heads*d + 2*heads*dv + 2*heads] and float32 output expected")
         if state.dtype != torch.float32 or state.dim() != 2 or state.shape[1] != heads * d * dv + heads * d + heads or state.stride(1) != 1:
             raise KernelError("mlstm_scan: state must be float32 [slots, heads*d*dv + heads*d + heads]")
-        self._call("hb_mlstm_scan", proj.data_ptr(), _code(proj), _rows(proj, "projections"),
+        if chunked is None:
+            chunked = step.max_new >= self.MLSTM_CHUNK_FROM
+        self._call("hb_mlstm_chunks" if chunked else "hb_mlstm_scan", proj.data_ptr(), _code(proj), _rows(proj, "projections"),
                    self._f32_vec(gate_bias, 2 * heads, "gate bias") if gate_bias is not None else None, float(cap), float(q_scale),
                    state.data_ptr(), state.stride(0), step.state_slots.data_ptr(), step.seq_start.data_ptr(), out.data_ptr(),
                    step.num_seqs, heads, d, dv, self._stream())

@@ -56,6 +56,7 @@ class SinkAttention(Mixer):
         self.proj_ld = (self.proj_width + 7) // 8 * 8
         self.out_width = self.heads * self.v_dim
         self.w_qkv = self.w_o = self.b_qkv = self.talk_matrix = self.v_lambda = None
+        self.use_heads_kernel = True          # tests switch it off to run the general kernel instead
 
     def params(self) -> List[ParamSpec]:
         W = self.hidden
@@ -123,11 +124,28 @@ class SinkAttention(Mixer):
         q = ws.buffer("sink_attention.q", (cap, self.q_width), self.ctx.dtype)[:T]
         ops.qkv_prepare(proj, self.b_qkv, table, rot, H, G, d, dv, self.qk_unit_norm, self.eps, q, cache, step, append,
                         self.v_lambda, v_first, v_mode)
-        all_values = self.talk and G > 1
-        n_val = G if all_values else 1
-        partial = ws.buffer("sink_attention.partial", (cap, H * n_val * dv), torch.float32)[:T]
-        ops.attention_sink(q, H, G, d, dv, cache, step, partial, self.scale, self.window, self.keep_first, all_values)
         ones = _BIAS_PAD if self.bias else 0
         attn = ws.buffer("sink_attention.out", (cap, self.out_width + ones), self.ctx.dtype)[:T]
-        ops.head_mix(partial, self.talk_matrix, attn, H, G, dv, n_val, ones)
+        longest = step.max_len if self.window is None else min(step.max_len, self.window + self.keep_first)
+        plan = ops.attention_heads_plan(T, H, G, d, dv, self.ctx.dtype, longest) if self.use_heads_kernel else None
+        if plan is not None:
+            # one block per (token, key split) serves all heads; it mixes the heads itself when it can
+            splits, writes_output = plan
+            if writes_output:
+                ops.attention_heads(q, H, G, d, dv, cache, step, self.scale, self.window, self.keep_first, 1,
+                                    mix=self.talk_matrix, out=attn, ones=ones)
+            else:
+                # tokens x splits at most: the same buffer for every step, a captured graph holds its address
+                rows = ops.ATTENTION_HEADS_MAX_ROWS if ops.attention_heads_whole(H, G, dv) else max(cap, ops.ATTENTION_HEADS_MAX_ROWS)
+                partial = ws.buffer("sink_attention.partial", (rows, H * G * dv), torch.float32)
+                ml = ws.buffer("sink_attention.ml", (rows, H * 2), torch.float32)
+                ops.attention_heads(q, H, G, d, dv, cache, step, self.scale, self.window, self.keep_first, splits,
+                                    partial=partial, ml=ml)
+                ops.head_mix_splits(partial, ml, self.talk_matrix, attn, H, G, dv, splits, ones)
+        else:
+            all_values = self.talk and G > 1
+            n_val = G if all_values else 1
+            partial = ws.buffer("sink_attention.partial_general", (cap, H * n_val * dv), torch.float32)[:T]
+            ops.attention_sink(q, H, G, d, dv, cache, step, partial, self.scale, self.window, self.keep_first, all_values)
+            ops.head_mix(partial, self.talk_matrix, attn, H, G, dv, n_val, ones)
         ops.linear(attn, self.w_o, residual, accumulate=True)

@@ -208,7 +208,7 @@ def test_short_convolution_carries_its_state_over_portions(taps, fused):
     require_gpu()
     C = 70
     ops, ws, cache, seqs = _ops_and_step([0, 0], [0, 0], [], max(1, (taps - 1) * C))
-    g = torch.Generator().manual_seed(taps)
+    g = torch.Generator().manual_seed(taps)   # (the cache of _ops_and_step holds 1024 tokens)
     total = [23, 9]
     x = [torch.randn(n, C, generator=g) * 2 for n in total]
     cw = (torch.randn(C, taps, generator=g) * 0.5).cuda()
@@ -243,14 +243,21 @@ def test_short_convolution_carries_its_state_over_portions(taps, fused):
         portion += 1
     for i in range(2):
         assert (torch.cat(got[i]).double() - want[i]).abs().max() < 2e-5
-    # a slot that is used again starts from zeros
+    # a slot that is used again starts from zeros; a long portion is cut over several blocks, then goes on
     for s in seqs:
         cache.close(s)
     again = cache.open()
-    step = _step(cache, ws, [again], [total[1]])
-    out = torch.empty(total[1], C, device="cuda")
-    ops.short_conv(x[1].cuda(), cw, state, step, out, norm=(nw, nb, na))
-    assert (out.cpu().double() - want[1]).abs().max() < 2e-5
+    long_x = torch.randn(700, C, generator=g) * 2
+    h = dyt(long_x.double(), nw.cpu().double(), nb.cpu().double(), 0.8)
+    long_want = h + causal_conv(h, cw.cpu().double())
+    at = 0
+    for n in (total[1], 600, 700 - 600 - total[1]):
+        step = _step(cache, ws, [again], [n])
+        out = torch.empty(n, C, device="cuda")
+        ops.short_conv(long_x[at: at + n].cuda(), cw, state, step, out, norm=(nw, nb, na))
+        assert (out.cpu().double() - long_want[at: at + n]).abs().max() < 2e-5
+        _commit(cache, [again], [n])
+        at += n
 
 
 @pytest.mark.gpu
@@ -262,7 +269,7 @@ def test_matrix_memory_in_portions_equals_the_scan(heads, d, dv):
     ops, ws, cache, seqs = _ops_and_step([0, 0], [0, 0], [], n_state)
     g = torch.Generator().manual_seed(d)
     width = 2 * H * d + 2 * H * dv + 2 * H
-    total = [40, 11]
+    total = [75, 11]
     proj = [torch.randn(n, width + 3, generator=g) for n in total]          # rows longer than what is read
     for p in proj:
         p[:, -2 * H - 3: -3] *= 3.0                                          # gates that reach their cap
@@ -283,7 +290,7 @@ def test_matrix_memory_in_portions_equals_the_scan(heads, d, dv):
         want.append(o * nw.double() * torch.sigmoid(gate))
     state = cache.state_view(0)
     got, done = [[], []], [0, 0]
-    for portion in (1, 2, 1, 5, 64):
+    for portion in (1, 2, 1, 5, 64, 8):     # portions of 8 tokens and more run the chunked kernel
         live = [i for i in range(2) if done[i] < total[i]]
         if not live:
             break
@@ -309,7 +316,7 @@ def test_matrix_memory_in_portions_equals_the_scan(heads, d, dv):
 @pytest.mark.gpu
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("H,G,d,dv,size,keep,rot", [(4, 2, 16, 8, 70, 3, 8), (2, 2, 8, 24, 64, 0, 8), (3, 1, 32, 16, 129, 65, 0),
-                                                     (6, 3, 64, 40, 5, 1, 32)])
+                                                     (6, 3, 64, 40, 5, 1, 32), (8, 4, 32, 256, 100, 2, 16), (3, 1, 20, 12, 40, 3, 4)])
 def test_attention_sees_exactly_the_window_and_the_first_tokens(H, G, d, dv, size, keep, rot, dtype):
     """A prompt of 300 tokens, then tokens one by one.  For some queries one key is made to stand
     out (its score dwarfs the others): the key just inside the window, just outside it, the last
@@ -365,6 +372,19 @@ def test_attention_sees_exactly_the_window_and_the_first_tokens(H, G, d, dv, siz
         ops.head_mix(partial, talk.reshape(-1).cuda(), out, H, G, dv, G, 8)
         assert torch.equal(out[:, H * dv:].float().cpu(), torch.tensor([1.0] + [0.0] * 7).expand(new, 8))
         got.append(out[:, : H * dv].float().cpu())
+        # the kernel that serves all heads of a token in one block: key splits combined afterwards, or the output at once
+        if ops.attention_heads_plan(new, H, G, d, dv, dtype, 10 ** 6) is not None:
+            for splits in (1, 3, 8):
+                part = torch.full((new * H * splits * G * dv,), float("nan"), device="cuda")
+                ml = torch.empty(new * H * splits * 2, device="cuda")
+                ops.attention_heads(qb, H, G, d, dv, view, step, scale, size, keep, splits, partial=part, ml=ml)
+                again = torch.empty_like(out)
+                ops.head_mix_splits(part, ml, talk.reshape(-1).cuda(), again, H, G, dv, splits, 8)
+                assert (again.float() - out.float()).abs().max().item() <= (1e-5 if dtype == torch.float32 else 2e-2) * max(1.0, out.float().abs().max().item())
+            if ops.attention_heads_whole(H, G, dv):
+                again = torch.empty_like(out)
+                ops.attention_heads(qb, H, G, d, dv, view, step, scale, size, keep, 1, mix=talk.reshape(-1).cuda(), out=again, ones=8)
+                assert (again.float() - out.float()).abs().max().item() <= (1e-5 if dtype == torch.float32 else 2e-2) * max(1.0, out.float().abs().max().item())
         _commit(cache, seqs, [new])
     ops.check_errors()
     got = torch.cat(got).double()
@@ -513,6 +533,27 @@ def test_fused_norm_and_convolution_equal_the_two_kernels(models, name):
     b = tt.run_in_process(eng, steps)
     for k in a:
         assert (a[k] - b[k]).abs().max() < 1e-4
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["mixed", "edges", "wide"])
+def test_attention_kernels_agree(models, name, dtype):
+    """The kernel that serves all heads per block (with key splits in decode steps) against the general one."""
+    require_gpu()
+    folder, cfg, plain = models[name]
+    v = cfg["vocab"]
+    batches = [{f"k{i}": (tt.random_tokens(n, v, 950 + i), p) for i, (n, p) in enumerate([(160, 150), (20, 3)])}]
+    steps, peak = tt.trace_batches(batches)
+    a = tt.run_in_process(_engine(folder, dtype, peak), steps)
+    eng = _engine(folder, dtype, peak)
+    for blk in eng.model.blocks:
+        if hasattr(blk.mixer, "use_heads_kernel"):
+            blk.mixer.use_heads_kernel = False
+    b = tt.run_in_process(eng, steps)
+    for k in a:
+        scale = max(1.0, b[k].abs().max().item())
+        assert (a[k] - b[k]).abs().max().item() <= (1e-4 if dtype == "float32" else 2e-2) * scale, k
 
 
 def _greedy(plain, prompt, n):
