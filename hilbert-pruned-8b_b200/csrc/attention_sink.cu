@@ -298,12 +298,12 @@ extern "C" int hb_head_mix(const float* partial, const float* mix, void* out, in
 // the weighted value sums a product [heads x keys] x [keys x (kv heads * v_dim)] per token.
 // Per tile of KT keys: scores by one thread per (kv head, key) for the heads of that group;
 // softmax bookkeeping by one warp per head (running maximum m, sum l, in float32); then every
-// thread adds the tile to its accumulators: 4 value columns for each of its heads.
+// thread adds the tile to its accumulators: 2 value columns for each of its heads, four keys at a time.
 // With one split and all heads of a column in one thread the block also mixes the heads and
 // writes the attention output; otherwise it writes unnormalised sums with (m, l) per head and
 // split, and head_mix combines splits and heads.
-#define AH_THREADS 256
-#define AH_CPT 4
+#define AH_THREADS 512
+#define AH_CPT 2
 
 template <typename TQ, typename TC, typename TO, int HPT, int KT>
 __global__ void __launch_bounds__(AH_THREADS)
@@ -447,19 +447,24 @@ attention_heads_kernel(const TQ* __restrict__ q, long long ldq, const TC* __rest
                     for (int j = 0; j < AH_CPT; j++) acc[i][j] *= c;
                 }
             }
-            const int n_keys = min(KT, v_end - v0);
-            for (int r = 0; r < n_keys; r++) {
-                float v[AH_CPT];
-                const TC* vr = Vs + (size_t)r * NC + col;
+            // rows beyond the split's last key hold zero weights and zero values: whole groups of four keys
+            const int n_keys = (min(KT, v_end - v0) + 3) & ~3;
+            for (int r = 0; r < n_keys; r += 4) {
+                float v[4][AH_CPT];
 #pragma unroll
-                for (int j = 0; j < AH_CPT; j++) v[j] = to_f32(vr[j]);
+                for (int x = 0; x < 4; x++) {
+                    const TC* vr = Vs + (size_t)(r + x) * NC + col;
+#pragma unroll
+                    for (int j = 0; j < AH_CPT; j++) v[x][j] = to_f32(vr[j]);
+                }
 #pragma unroll
                 for (int i = 0; i < HPT; i++) {
                     const int h = my_hg + i * hg;
                     if (h < nh) {
-                        const float pe = Ss[h * KT + r];
+                        const float4 pe = *reinterpret_cast<const float4*>(Ss + h * KT + r);
 #pragma unroll
-                        for (int j = 0; j < AH_CPT; j++) acc[i][j] = fmaf(pe, v[j], acc[i][j]);
+                        for (int j = 0; j < AH_CPT; j++)
+                            acc[i][j] = fmaf(pe.w, v[3][j], fmaf(pe.z, v[2][j], fmaf(pe.y, v[1][j], fmaf(pe.x, v[0][j], acc[i][j]))));
                     }
                 }
             }
@@ -471,7 +476,9 @@ attention_heads_kernel(const TQ* __restrict__ q, long long ldq, const TC* __rest
         if (works && col < NC) {
             const int c = col / vd, d = col - c * vd;
             for (int h2 = c * group; h2 < (c + 1) * group; h2++) {
-                float o[AH_CPT] = {0.0f, 0.0f, 0.0f, 0.0f};
+                float o[AH_CPT];
+#pragma unroll
+                for (int j = 0; j < AH_CPT; j++) o[j] = 0.0f;
 #pragma unroll
                 for (int i = 0; i < HPT; i++) {
                     if (i < nh) {
@@ -493,7 +500,8 @@ attention_heads_kernel(const TQ* __restrict__ q, long long ldq, const TC* __rest
             const int h = my_hg + i * hg;
             if (h < nh) {
                 float* o = partial + (((size_t)t * nh + h) * splits + split) * NC + col;
-                *reinterpret_cast<float4*>(o) = make_float4(acc[i][0], acc[i][1], acc[i][2], acc[i][3]);
+#pragma unroll
+                for (int j = 0; j < AH_CPT; j++) o[j] = acc[i][j];
             }
         }
     }

@@ -146,8 +146,9 @@ extern "C" int hb_mlstm_scan(const void* proj, int proj_dtype, long long ldp, co
 // The tokens of a chunk no longer wait for one another: one pass over S0 serves L tokens, and the state moves once
 // per chunk.  All in float32.  One block per (32 value columns, head, sequence), 4 warps, lane = value column.
 #define MC_L 32
+#define MC_WARPS 16           // sixteen warps: two tokens of a chunk each; the kernel waits on shared memory, more warps hide it
 template <typename TP>
-__global__ void __launch_bounds__(ML_VS * ML_WARPS)
+__global__ void __launch_bounds__(ML_VS * MC_WARPS)
 mlstm_chunks_kernel(const TP* __restrict__ proj, long long ldp, const float* __restrict__ gate_bias, float cap, float q_scale,
                     float* __restrict__ state, long long state_stride, const int* __restrict__ state_slots,
                     const int* __restrict__ seq_start, float* __restrict__ out, int nh, int d, int dv, int L) {
@@ -182,8 +183,8 @@ mlstm_chunks_kernel(const TP* __restrict__ proj, long long ldp, const float* __r
     pdl_wait();
     proj = pdl_fresh(proj);
     base = pdl_fresh(base);
-    for (int r = warp; r < d; r += ML_WARPS) S[r * ML_VS + lane] = has_col ? gS[(size_t)r * dv + col] : 0.0f;
-    for (int r = tid; r < d; r += ML_VS * ML_WARPS) ns[r] = gn[r];
+    for (int r = warp; r < d; r += MC_WARPS) S[r * ML_VS + lane] = has_col ? gS[(size_t)r * dv + col] : 0.0f;
+    for (int r = tid; r < d; r += ML_VS * MC_WARPS) ns[r] = gn[r];
     if (tid == 0) m_shared = gm[0];
     __syncthreads();
 
@@ -192,7 +193,7 @@ mlstm_chunks_kernel(const TP* __restrict__ proj, long long ldp, const float* __r
         const float m0 = m_shared;
         // 1. the chunk's q (scaled), k, v and gates.  Two token rows per warp at a time, four values of q and of k
         // per lane and row: sixteen loads in flight per thread before the first is stored.
-        for (int j0 = 2 * warp; j0 < nc; j0 += 2 * ML_WARPS) {
+        for (int j0 = 2 * warp; j0 < nc; j0 += 2 * MC_WARPS) {
             for (int r0 = lane; r0 < d; r0 += 128) {
                 float qv[2][4], kv[2][4];
 #pragma unroll
@@ -219,15 +220,15 @@ mlstm_chunks_kernel(const TP* __restrict__ proj, long long ldp, const float* __r
             }
         }
         {
-            float vv[MC_L / ML_WARPS];
+            float vv[MC_L / MC_WARPS];
 #pragma unroll
-            for (int i = 0; i < MC_L / ML_WARPS; i++) {
-                const int j = min(warp + i * ML_WARPS, nc - 1);
+            for (int i = 0; i < MC_L / MC_WARPS; i++) {
+                const int j = min(warp + i * MC_WARPS, nc - 1);
                 vv[i] = has_col ? to_f32(proj[(size_t)(start + c0 + j) * ldp + off_v + h * dv + col]) : 0.0f;
             }
 #pragma unroll
-            for (int i = 0; i < MC_L / ML_WARPS; i++) {
-                const int j = warp + i * ML_WARPS;
+            for (int i = 0; i < MC_L / MC_WARPS; i++) {
+                const int j = warp + i * MC_WARPS;
                 if (j < nc) vs[j * ML_VS + lane] = vv[i];
             }
         }
@@ -265,7 +266,7 @@ mlstm_chunks_kernel(const TP* __restrict__ proj, long long ldp, const float* __r
         }
         __syncthreads();
         // 3. W[j][s]
-        for (int i = tid; i < nc * nc; i += ML_VS * ML_WARPS) {
+        for (int i = tid; i < nc * nc; i += ML_VS * MC_WARPS) {
             const int j = i / nc, sidx = i - j * nc;
             float w = 0.0f;
             if (sidx <= j) {
@@ -278,22 +279,22 @@ mlstm_chunks_kernel(const TP* __restrict__ proj, long long ldp, const float* __r
             W[j * L + sidx] = w;
         }
         __syncthreads();
-        // 4. outputs: warp w takes the tokens w, w + 4, ...
+        // 4. outputs: warp w takes the tokens w, w + 16
         {
-            float acc[MC_L / ML_WARPS], nq[MC_L / ML_WARPS];
+            float acc[MC_L / MC_WARPS], nq[MC_L / MC_WARPS];
 #pragma unroll
-            for (int i = 0; i < MC_L / ML_WARPS; i++) acc[i] = 0.0f, nq[i] = 0.0f;
+            for (int i = 0; i < MC_L / MC_WARPS; i++) acc[i] = 0.0f, nq[i] = 0.0f;
             for (int r = 0; r < d; r++) {
                 const float sv = S[r * ML_VS + lane];
 #pragma unroll
-                for (int i = 0; i < MC_L / ML_WARPS; i++) {
-                    const int j = warp + i * ML_WARPS;
+                for (int i = 0; i < MC_L / MC_WARPS; i++) {
+                    const int j = warp + i * MC_WARPS;
                     if (j < nc) acc[i] = fmaf(sv, qs[j * dp + r], acc[i]);
                 }
             }
 #pragma unroll
-            for (int i = 0; i < MC_L / ML_WARPS; i++) {
-                const int j = warp + i * ML_WARPS;
+            for (int i = 0; i < MC_L / MC_WARPS; i++) {
+                const int j = warp + i * MC_WARPS;
                 if (j < nc) {
                     float p = 0.0f;
                     for (int r = lane; r < d; r += 32) p = fmaf(ns[r], qs[j * dp + r], p);
@@ -305,14 +306,14 @@ mlstm_chunks_kernel(const TP* __restrict__ proj, long long ldp, const float* __r
             for (int sidx = 0; sidx < nc; sidx++) {
                 const float vv = vs[sidx * ML_VS + lane];
 #pragma unroll
-                for (int i = 0; i < MC_L / ML_WARPS; i++) {
-                    const int j = warp + i * ML_WARPS;
+                for (int i = 0; i < MC_L / MC_WARPS; i++) {
+                    const int j = warp + i * MC_WARPS;
                     if (j < nc) acc[i] = fmaf(W[j * L + sidx], vv, acc[i]);
                 }
             }
 #pragma unroll
-            for (int i = 0; i < MC_L / ML_WARPS; i++) {
-                const int j = warp + i * ML_WARPS;
+            for (int i = 0; i < MC_L / MC_WARPS; i++) {
+                const int j = warp + i * MC_WARPS;
                 if (j < nc && has_col) {
                     const float den = fmaxf(fabsf(nq[i]), em_s[j]) + 1e-6f;
                     out[(size_t)(start + c0 + j) * nh * dv + (size_t)h * dv + col] = acc[i] / den;
@@ -326,14 +327,14 @@ mlstm_chunks_kernel(const TP* __restrict__ proj, long long ldp, const float* __r
             float wv[MC_L];
 #pragma unroll
             for (int sidx = 0; sidx < MC_L; sidx++) wv[sidx] = sidx < nc ? Dl_s[sidx] * vs[sidx * ML_VS + lane] : 0.0f;
-            for (int r = warp; r < d; r += ML_WARPS) {
+            for (int r = warp; r < d; r += MC_WARPS) {
                 float sv = g_last * S[r * ML_VS + lane];
 #pragma unroll
                 for (int sidx = 0; sidx < MC_L; sidx++)
                     if (sidx < nc) sv = fmaf(ks[sidx * dp + r], wv[sidx], sv);
                 S[r * ML_VS + lane] = sv;
             }
-            for (int r = tid; r < d; r += ML_VS * ML_WARPS) {
+            for (int r = tid; r < d; r += ML_VS * MC_WARPS) {
                 float nv = g_last * ns[r];
                 for (int sidx = 0; sidx < nc; sidx++) nv = fmaf(Dl_s[sidx], ks[sidx * dp + r], nv);
                 ns[r] = nv;
@@ -342,10 +343,10 @@ mlstm_chunks_kernel(const TP* __restrict__ proj, long long ldp, const float* __r
         __syncthreads();
     }
     if (n_tok > 0) {
-        for (int r = warp; r < d; r += ML_WARPS)
+        for (int r = warp; r < d; r += MC_WARPS)
             if (has_col) gS[(size_t)r * dv + col] = S[r * ML_VS + lane];
         if (blockIdx.x == 0) {
-            for (int r = tid; r < d; r += ML_VS * ML_WARPS) gn[r] = ns[r];
+            for (int r = tid; r < d; r += ML_VS * MC_WARPS) gn[r] = ns[r];
             if (tid == 0) gm[0] = m_shared;
         }
     }
@@ -374,7 +375,7 @@ extern "C" int hb_mlstm_chunks(const void* proj, int proj_dtype, long long ldp, 
         done[hb_device_slot()] = true;
     }
     dim3 grid((dv + ML_VS - 1) / ML_VS, n_heads, n_seqs);
-    hb_launch(mlstm_chunks_kernel<float>, dim3(grid), dim3(ML_VS * ML_WARPS), smem, (cudaStream_t)stream, (const float*)proj, ldp, gate_bias,
+    hb_launch(mlstm_chunks_kernel<float>, dim3(grid), dim3(ML_VS * MC_WARPS), smem, (cudaStream_t)stream, (const float*)proj, ldp, gate_bias,
               cap, q_scale, state, state_stride, state_slots, seq_start, out, n_heads, d, dv, L);
     return hb_check_launch("mlstm_chunks");
 }

@@ -17,7 +17,10 @@ import os
 import sys
 from typing import Dict, IO
 
+from ..cache.manager import PAGE_TOKENS
 from .batch import StepEntry
+
+PAGE_SLACK = 128
 
 
 def replay(engine, lines: IO[str], out_dir: str, reply: IO[str]) -> int:
@@ -59,14 +62,17 @@ def main(argv=None) -> int:
     ap.add_argument("--dtype", choices=("bfloat16", "float32"), default="bfloat16")
     ap.add_argument("--out", required=True, help="folder that receives <step>.f32")
     ap.add_argument("--max-tokens", type=int, required=True,
-                    help="most tokens live requests hold at any time (each rounded up to 64); sizes the cache")
+                    help="most tokens live requests hold at any time; sizes the cache (which adds room for the unused "
+                         "ends of the requests' last pages)")
     ap.add_argument("--device", type=int, default=0)
     args = ap.parse_args(argv)
     if args.max_tokens < 1:
         ap.error("--max-tokens must be positive")
     from .step import Engine
     try:
-        engine = Engine.from_folder(args.model, args.dtype, max_tokens=args.max_tokens, device=f"cuda:{args.device}")
+        # a request holds whole pages: up to PAGE_SLACK live requests may each leave most of a page unused
+        engine = Engine.from_folder(args.model, args.dtype, max_tokens=args.max_tokens + PAGE_SLACK * PAGE_TOKENS,
+                                    device=f"cuda:{args.device}")
         return replay(engine, sys.stdin, args.out, sys.stdout)
     except (ValueError, RuntimeError) as e:        # configuration, weights, a refused step, a fault a kernel noted
         print(f"error: {e}", file=sys.stderr)

@@ -509,7 +509,7 @@ class Ops:
     @staticmethod
     def attention_heads_whole(heads: int, kv_heads: int, v_dim: int) -> bool:
         """Whether one thread of ``attention_heads`` holds every head of its value columns (the block can then mix the heads)."""
-        return min(256 // (-(-kv_heads * v_dim // 4)), heads) == 1
+        return min(512 // (-(-kv_heads * v_dim // 2)), heads) == 1
 
     def attention_heads_plan(self, tokens: int, heads: int, kv_heads: int, head_dim: int, v_dim: int, dtype, longest: int):
         """How ``attention_heads`` would run a step, or None when its kernel is not built for these sizes:
@@ -519,9 +519,13 @@ class Ops:
         if not self.lib.hb_attention_heads_variant(heads, kv_heads, head_dim, v_dim, _DTYPE_CODE[dtype]):
             return None
         whole = self.attention_heads_whole(heads, kv_heads, v_dim)
+        # the kernel that combines the splits keeps [heads, splits + v_dim] floats in 48 KB of shared memory
+        most = (48 * 1024 // 4 - heads * v_dim) // heads
+        if most < 1 and not whole:
+            return None
         splits = 1
         if tokens < self.sm_count:
-            splits = max(1, min(-(-self.sm_count // tokens), longest // 64, 32))
+            splits = max(1, min(-(-self.sm_count // tokens), longest // 64, 32, most))
         return splits, (splits == 1 and whole)
 
     def attention_heads(self, q, heads: int, kv_heads: int, head_dim: int, v_dim: int, cache, step, scale: float, window: Optional[int],
