@@ -107,6 +107,83 @@ short_conv_kernel(const float* __restrict__ x, const float* __restrict__ nw, con
     }
 }
 
+// The same with the number of taps known at compile time (1..8): a thread walks SC_RUN / SC_TL consecutive tokens and
+// keeps the last TAPS inputs in registers, so every input is normed once (the general kernel above norms it once per tap).
+template <typename TO, bool NORM, int TAPS>
+__global__ void __launch_bounds__(SC_CH * SC_TL)
+short_conv_taps_kernel(const float* __restrict__ x, const float* __restrict__ nw, const float* __restrict__ nb,
+                       const float* __restrict__ nalpha, const float* __restrict__ cw, float* __restrict__ state,
+                       long long state_stride, const int* __restrict__ state_slots, const int* __restrict__ seq_start,
+                       TO* __restrict__ out, long long ldo, int C) {
+    pdl_trigger();
+    constexpr int HIST = TAPS - 1, PER = SC_RUN / SC_TL;
+    const int c = blockIdx.x * SC_CH + (threadIdx.x & (SC_CH - 1));
+    const int tl = threadIdx.x / SC_CH;
+    const int b = blockIdx.y;
+    const bool live = c < C;
+    float w[TAPS], st[TAPS];            // st[HIST] unused: arrays of TAPS - 1 elements would be empty for one tap
+    float a = 0.0f, gw = 0.0f, gb = 0.0f;
+#pragma unroll
+    for (int j = 0; j < TAPS; j++) w[j] = live ? cw[(size_t)c * TAPS + j] : 0.0f;
+    if (NORM) {
+        a = nalpha[0];
+        gw = live ? nw[c] : 0.0f;
+        gb = live ? nb[c] : 0.0f;
+    }
+    const int start = seq_start[b], n = seq_start[b + 1] - start;
+    const int t_begin = blockIdx.z * SC_RUN, t_end = min(n, t_begin + SC_RUN);
+    if (t_begin >= n) return;
+    const bool first = blockIdx.z == 0;
+    float* srow = state + (size_t)state_slots[b] * state_stride;
+    pdl_wait();
+    x = pdl_fresh(x);
+    srow = pdl_fresh(srow);
+#pragma unroll
+    for (int j = 0; j < TAPS; j++) st[j] = (first && live && j < HIST) ? srow[(size_t)j * C + c] : 0.0f;
+    __syncthreads();
+    auto input = [&](int src) -> float {
+        if (src < 0) {
+            float v = 0.0f;
+#pragma unroll
+            for (int j = 0; j < TAPS; j++) v = (j == HIST + src) ? st[j] : v;
+            return v;
+        }
+        const float xv = x[(size_t)(start + src) * C + c];
+        return NORM ? fmaf(tanhf(a * xv), gw, gb) : xv;
+    };
+    if (!live) return;
+    const int t0 = t_begin + tl * PER, t1 = min(t_end, t0 + PER);
+    if (t0 < t1) {
+        float win[TAPS];
+#pragma unroll
+        for (int j = 0; j < HIST; j++) win[j] = input(t0 - HIST + j);
+        for (int t = t0; t < t1; t++) {
+            const float h = input(t);
+            win[HIST] = h;
+            float acc = 0.0f;
+#pragma unroll
+            for (int j = 0; j < TAPS; j++) acc = fmaf(w[j], win[j], acc);
+            out[(size_t)(start + t) * ldo + c] = from_f32<TO>(h + acc);
+#pragma unroll
+            for (int j = 0; j < HIST; j++) win[j] = win[j + 1];
+        }
+    }
+    if (first && tl == 0) {
+#pragma unroll
+        for (int j = 0; j < HIST; j++) srow[(size_t)j * C + c] = input(n - HIST + j);
+    }
+}
+
+template <typename TO, bool NORM>
+static void short_conv_taps_launch(int taps, dim3 grid, dim3 block, cudaStream_t s, const float* x, const float* nw, const float* nb,
+                                   const float* na, const float* cw, float* state, long long state_stride, const int* state_slots,
+                                   const int* seq_start, void* out, long long ldo, int C) {
+#define HB_SCT(T) case T: hb_launch(short_conv_taps_kernel<TO, NORM, T>, dim3(grid), dim3(block), 0, s, x, nw, nb, na, cw, state, state_stride,   \
+                                    state_slots, seq_start, (TO*)out, ldo, C); break;
+    switch (taps) { HB_SCT(1) HB_SCT(2) HB_SCT(3) HB_SCT(4) HB_SCT(5) HB_SCT(6) HB_SCT(7) HB_SCT(8) }
+#undef HB_SCT
+}
+
 extern "C" int hb_short_conv(const float* x, const float* norm_w, const float* norm_b, const float* norm_alpha,
                              const float* conv_w, int taps, float* state, long long state_stride, const int* state_slots,
                              const int* seq_start, void* out, int out_dtype, long long ldo, int n_seqs, int max_new, int C,
@@ -123,6 +200,16 @@ extern "C" int hb_short_conv(const float* x, const float* norm_w, const float* n
     hb_launch(short_conv_kernel<TO, NORM>, dim3(grid), dim3(block), 0, s, x, norm_w, norm_b, norm_alpha, conv_w, taps, state,           \
               state_stride, state_slots, seq_start, (TO*)out, ldo, C)
     const bool norm = norm_w != nullptr;
+    if (taps <= 8 && (out_dtype == HB_BF16 || out_dtype == HB_F32)) {
+        if (out_dtype == HB_BF16) {
+            if (norm) short_conv_taps_launch<bf16, true>(taps, grid, block, s, x, norm_w, norm_b, norm_alpha, conv_w, state, state_stride, state_slots, seq_start, out, ldo, C);
+            else short_conv_taps_launch<bf16, false>(taps, grid, block, s, x, norm_w, norm_b, norm_alpha, conv_w, state, state_stride, state_slots, seq_start, out, ldo, C);
+        } else {
+            if (norm) short_conv_taps_launch<float, true>(taps, grid, block, s, x, norm_w, norm_b, norm_alpha, conv_w, state, state_stride, state_slots, seq_start, out, ldo, C);
+            else short_conv_taps_launch<float, false>(taps, grid, block, s, x, norm_w, norm_b, norm_alpha, conv_w, state, state_stride, state_slots, seq_start, out, ldo, C);
+        }
+        return hb_check_launch("short_conv");
+    }
     if (out_dtype == HB_BF16) { if (norm) HB_SC_LAUNCH(bf16, true); else HB_SC_LAUNCH(bf16, false); }
     else if (out_dtype == HB_F32) { if (norm) HB_SC_LAUNCH(float, true); else HB_SC_LAUNCH(float, false); }
     else return hb_fail("short_conv: unsupported output dtype %d", out_dtype);
