@@ -119,11 +119,13 @@ int hb_attention_sink(const void* q, int q_dtype, long long ldq, const void* k_c
 int hb_head_mix(const float* partial, const float* mix, void* out, int out_dtype, long long ldo, int n_tokens, int n_heads,
                 int n_kv_heads, int v_dim, int n_val, int ones, void* stream);
 // One block per (token, key split) for all heads; see attention_sink.cu.  hb_attention_heads_variant: 0 when the sizes are not built.
-int hb_attention_heads_variant(int n_heads, int n_kv_heads, int head_dim, int v_dim, int cache_dtype);
+int hb_attention_heads_variant(int n_heads, int n_kv_heads, int head_dim, int v_dim, int cache_dtype, int allow_mma);
+int hb_attention_heads_writes_output(int n_heads, int n_kv_heads, int head_dim, int v_dim, int cache_dtype, int allow_mma);
 int hb_attention_heads(const void* q, int q_dtype, long long ldq, const void* k_cache, const void* v_cache, int cache_dtype,
                        const int* page_table, int pt_width, const int* tok_seq, const int* positions, float* partial, float* ml,
                        const float* mix, void* out, long long ldo, int ones, int n_tokens, int n_heads, int n_kv_heads, int head_dim,
-                       int v_dim, float scale, int window, int keep_first, int splits, int n_pages, int* status, void* stream);
+                       int v_dim, float scale, int window, int keep_first, int splits, int n_pages, int allow_mma, int* status,
+                       void* stream);
 int hb_head_mix_splits(const float* partial, const float* ml, const float* mix, void* out, int out_dtype, long long ldo, int n_tokens,
                        int n_heads, int n_kv_heads, int v_dim, int splits, int ones, void* stream);
 // proj rows: [q heads*d | k heads*d | v heads*dv | gate heads*dv | z_i heads | z_f heads]; state per slot:

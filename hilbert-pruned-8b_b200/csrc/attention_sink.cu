@@ -15,6 +15,7 @@
 //    weights, applied to the values, is the same mix of their weighted value sums.
 #include "api.h"
 #include "common.cuh"
+#include "mma.cuh"
 
 #define QP_THREADS 128
 #define QP_MAX_HD 512
@@ -302,10 +303,15 @@ extern "C" int hb_head_mix(const float* partial, const float* mix, void* out, in
 // With one split and all heads of a column in one thread the block also mixes the heads and
 // writes the attention output; otherwise it writes unnormalised sums with (m, l) per head and
 // split, and head_mix combines splits and heads.
+// MMA variant (bfloat16 cache, 16 or 32 heads, up to 1024 value columns): the product of the tile's weights
+// [heads x keys] with its values [keys x columns] runs on the tensor cores (mma.sync m16n8k16).  The weights
+// are 32-bit; each is handed over as TWO bfloat16 terms, hi = bf16(p) and lo = bf16(p - hi), and the two
+// products are added in the 32-bit accumulator: p is then exact to 16 mantissa bits (relative 2^-17), far
+// below the rounding of the bfloat16 values it multiplies.  Scores, maxima, sums and mixing stay FP32 code.
 #define AH_THREADS 512
 #define AH_CPT 2
 
-template <typename TQ, typename TC, typename TO, int HPT, int KT>
+template <typename TQ, typename TC, typename TO, int HPT, int KT, bool MMA>
 __global__ void __launch_bounds__(AH_THREADS)
 attention_heads_kernel(const TQ* __restrict__ q, long long ldq, const TC* __restrict__ k_cache, const TC* __restrict__ v_cache,
                        const int* __restrict__ page_table, int pt_width, const int* __restrict__ tok_seq,
@@ -315,7 +321,7 @@ attention_heads_kernel(const TQ* __restrict__ q, long long ldq, const TC* __rest
     pdl_trigger();
     constexpr int CE = 16 / (int)sizeof(TC);            // cache elements per 16-byte piece
     extern __shared__ __align__(16) unsigned char ah_smem[];
-    const int NC = nkv * vd, kst = nkv * hd + CE;       // key rows are padded by 16 bytes against bank conflicts
+    const int NC = nkv * vd, kst = nkv * hd + CE, vst = NC + CE;   // rows are padded by 16 bytes against bank conflicts
     float* qs = reinterpret_cast<float*>(ah_smem);      // [nh][hd]
     float* Ss = qs + nh * hd;                           // [nh][KT]
     float* m_s = Ss + nh * KT;                          // [nh]
@@ -325,6 +331,9 @@ attention_heads_kernel(const TQ* __restrict__ q, long long ldq, const TC* __rest
     int* page_of = key_of + KT;
     TC* Ks = reinterpret_cast<TC*>(page_of + KT + ((4 - ((nh * hd + nh * KT + 3 * nh + 2 * KT) & 3)) & 3));
     TC* Vs = Ks + (size_t)KT * kst;
+    constexpr int PST = KT + 8;                         // row stride of the weights' two bfloat16 terms
+    bf16* Ph = reinterpret_cast<bf16*>(Vs + (size_t)KT * vst);      // [nh][PST] (MMA only)
+    bf16* Pl = Ph + nh * PST;
 
     const int t = blockIdx.x, split = blockIdx.y, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int p = positions[t];
@@ -347,6 +356,17 @@ attention_heads_kernel(const TQ* __restrict__ q, long long ldq, const TC* __rest
     for (int i = 0; i < HPT; i++)
 #pragma unroll
         for (int j = 0; j < AH_CPT; j++) acc[i][j] = 0.0f;
+    // MMA: warp w owns the pairs of 8-column tiles w, w + 16, ... (up to 4); [row tile of 16 heads][pair][tile][fragment]
+    float cacc[2][4][2][4];
+#pragma unroll
+    for (int a = 0; a < 2; a++)
+#pragma unroll
+        for (int b2 = 0; b2 < 4; b2++)
+#pragma unroll
+            for (int c2 = 0; c2 < 2; c2++)
+#pragma unroll
+                for (int e = 0; e < 4; e++) cacc[a][b2][c2][e] = 0.0f;
+    const int MT = nh >> 4, n_pairs = NC >> 4, r0 = lane >> 2;
 
     pdl_wait();
     q = pdl_fresh(q);
@@ -401,7 +421,7 @@ attention_heads_kernel(const TQ* __restrict__ q, long long ldq, const TC* __rest
             }
         };
         copy_rows(k_cache, Ks, hd, kst, kcpr);
-        copy_rows(v_cache, Vs, vd, NC, vcpr);
+        copy_rows(v_cache, Vs, vd, vst, vcpr);
         __syncthreads();
         // scores: thread (kv head, key), the heads of the group one after the other
         for (int i = tid; i < nkv * KT; i += AH_THREADS) {
@@ -428,7 +448,14 @@ attention_heads_kernel(const TQ* __restrict__ q, long long ldq, const TC* __rest
             const float m_new = fmaxf(m_old, warp_max(s));
             const float pr = (s == -INFINITY) ? 0.0f : expf(s - m_new);
             const float sum = warp_sum(pr);
-            if (lane < KT) Ss[h * KT + lane] = pr;
+            if (lane < KT) {
+                Ss[h * KT + lane] = pr;
+                if (MMA) {
+                    const bf16 hi = __float2bfloat16_rn(pr);
+                    Ph[h * PST + lane] = hi;
+                    Pl[h * PST + lane] = __float2bfloat16_rn(pr - __bfloat162float(hi));
+                }
+            }
             if (lane == 0) {
                 const float corr = (m_old == -INFINITY) ? 0.0f : expf(m_old - m_new);
                 m_s[h] = m_new;
@@ -437,7 +464,56 @@ attention_heads_kernel(const TQ* __restrict__ q, long long ldq, const TC* __rest
             }
         }
         __syncthreads();
-        if (works && col < NC) {
+        if (MMA) {
+#pragma unroll
+            for (int mt = 0; mt < 2; mt++) {
+                if (mt < MT) {
+                    const float c0 = c_s[mt * 16 + r0], c1 = c_s[mt * 16 + r0 + 8];
+#pragma unroll
+                    for (int i = 0; i < 4; i++)
+#pragma unroll
+                        for (int hf = 0; hf < 2; hf++) {
+                            cacc[mt][i][hf][0] *= c0;
+                            cacc[mt][i][hf][1] *= c0;
+                            cacc[mt][i][hf][2] *= c1;
+                            cacc[mt][i][hf][3] *= c1;
+                        }
+                }
+            }
+            const uint32_t ph_base = (uint32_t)__cvta_generic_to_shared(Ph), pl_base = (uint32_t)__cvta_generic_to_shared(Pl);
+            const uint32_t v_base = (uint32_t)__cvta_generic_to_shared(Vs);
+            const int a_row = (lane & 7) + ((lane >> 3) & 1) * 8, a_col = (lane >> 4) * 8;
+            const int v_row = ((lane >> 3) & 1) * 8 + (lane & 7), v_chunk = lane >> 4;
+#pragma unroll
+            for (int ks = 0; ks < KT / 16; ks++) {
+                uint32_t ah[2][4], al[2][4];
+#pragma unroll
+                for (int mt = 0; mt < 2; mt++) {
+                    if (mt < MT) {
+                        const uint32_t off = (uint32_t)(((mt * 16 + a_row) * PST + ks * 16 + a_col) * 2);
+                        ldmatrix_x4(ah[mt], ph_base + off);
+                        ldmatrix_x4(al[mt], pl_base + off);
+                    }
+                }
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    const int pr2 = warp + 16 * i;
+                    if (pr2 < n_pairs) {
+                        uint32_t vf[4];
+                        ldmatrix_x4_trans(vf, v_base + (uint32_t)(((ks * 16 + v_row) * vst + pr2 * 16 + v_chunk * 8) * 2));
+#pragma unroll
+                        for (int mt = 0; mt < 2; mt++) {
+                            if (mt < MT) {
+                                mma_bf16_16816(cacc[mt][i][0], ah[mt], vf[0], vf[1]);
+                                mma_bf16_16816(cacc[mt][i][0], al[mt], vf[0], vf[1]);
+                                mma_bf16_16816(cacc[mt][i][1], ah[mt], vf[2], vf[3]);
+                                mma_bf16_16816(cacc[mt][i][1], al[mt], vf[2], vf[3]);
+                            }
+                        }
+                    }
+                }
+            }
+        } else if (works && col < NC) {
 #pragma unroll
             for (int i = 0; i < HPT; i++) {
                 const int h = my_hg + i * hg;
@@ -453,7 +529,7 @@ attention_heads_kernel(const TQ* __restrict__ q, long long ldq, const TC* __rest
                 float v[4][AH_CPT];
 #pragma unroll
                 for (int x = 0; x < 4; x++) {
-                    const TC* vr = Vs + (size_t)(r + x) * NC + col;
+                    const TC* vr = Vs + (size_t)(r + x) * vst + col;
 #pragma unroll
                     for (int j = 0; j < AH_CPT; j++) v[x][j] = to_f32(vr[j]);
                 }
@@ -471,6 +547,64 @@ attention_heads_kernel(const TQ* __restrict__ q, long long ldq, const TC* __rest
         }
     }
     __syncthreads();
+    if (MMA) {
+        // the accumulators: rows (heads) r0, r0 + 8 of each row tile, columns (lane & 3) * 2 + {0, 1} of each 8-column tile
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            const int pr2 = warp + 16 * i;
+            if (pr2 >= n_pairs) continue;                   // the same for the whole warp
+#pragma unroll
+            for (int hf = 0; hf < 2; hf++) {
+                const int n0 = pr2 * 16 + hf * 8, cc = (lane & 3) * 2;
+                if (out != nullptr) {
+                    const int cv = n0 / vd, d0 = n0 - cv * vd + cc;     // an 8-column tile lies inside one value head
+                    for (int h2 = cv * group; h2 < (cv + 1) * group; h2++) {
+                        float s0 = 0.0f, s1 = 0.0f;
+#pragma unroll
+                        for (int mt = 0; mt < 2; mt++) {
+                            if (mt < MT) {
+                                const int g0 = mt * 16 + r0, g1 = g0 + 8;
+                                const float w0 = (mix ? mix[h2 * nh + g0] : (g0 == h2 ? 1.0f : 0.0f)) / l_s[g0];
+                                const float w1 = (mix ? mix[h2 * nh + g1] : (g1 == h2 ? 1.0f : 0.0f)) / l_s[g1];
+                                s0 = fmaf(w1, cacc[mt][i][hf][2], fmaf(w0, cacc[mt][i][hf][0], s0));
+                                s1 = fmaf(w1, cacc[mt][i][hf][3], fmaf(w0, cacc[mt][i][hf][1], s1));
+                            }
+                        }
+#pragma unroll
+                        for (int o = 4; o < 32; o <<= 1) {
+                            s0 += __shfl_xor_sync(0xffffffffu, s0, o);
+                            s1 += __shfl_xor_sync(0xffffffffu, s1, o);
+                        }
+                        if (r0 == 0) {
+                            out[(size_t)t * ldo + h2 * vd + d0] = from_f32<TO>(s0);
+                            out[(size_t)t * ldo + h2 * vd + d0 + 1] = from_f32<TO>(s1);
+                        }
+                    }
+                } else {
+#pragma unroll
+                    for (int mt = 0; mt < 2; mt++) {
+                        if (mt < MT) {
+                            const int g0 = mt * 16 + r0, g1 = g0 + 8;
+                            float* o0 = partial + (((size_t)t * nh + g0) * splits + split) * NC + n0 + cc;
+                            float* o1 = partial + (((size_t)t * nh + g1) * splits + split) * NC + n0 + cc;
+                            *reinterpret_cast<float2*>(o0) = make_float2(cacc[mt][i][hf][0], cacc[mt][i][hf][1]);
+                            *reinterpret_cast<float2*>(o1) = make_float2(cacc[mt][i][hf][2], cacc[mt][i][hf][3]);
+                        }
+                    }
+                }
+            }
+        }
+        if (out != nullptr) {
+            for (int e = tid; e < ones; e += AH_THREADS) out[(size_t)t * ldo + nh * vd + e] = from_f32<TO>(e == 0 ? 1.0f : 0.0f);
+        } else {
+            for (int h = tid; h < nh; h += AH_THREADS) {
+                float* o = ml + (((size_t)t * nh + h) * splits + split) * 2;
+                o[0] = m_s[h];
+                o[1] = l_s[h];
+            }
+        }
+        return;
+    }
     if (out != nullptr) {
         // one split, every head of these columns in this thread: normalise, mix the heads, write the output
         if (works && col < NC) {
@@ -512,37 +646,52 @@ attention_heads_kernel(const TQ* __restrict__ q, long long ldq, const TC* __rest
     }
 }
 
-static size_t ah_smem_bytes(int nh, int nkv, int hd, int vd, int kt, int cache_elem) {
+static size_t ah_smem_bytes(int nh, int nkv, int hd, int vd, int kt, int cache_elem, bool mma) {
     const int ce = 16 / cache_elem;
     size_t words = (size_t)nh * hd + (size_t)nh * kt + 3 * (size_t)nh + 2 * (size_t)kt;
     words = (words + 3) & ~(size_t)3;
-    return words * 4 + ((size_t)kt * (nkv * hd + ce) + (size_t)kt * nkv * vd) * cache_elem;
+    return words * 4 + ((size_t)kt * (nkv * hd + ce) + (size_t)kt * (nkv * vd + ce)) * cache_elem + (mma ? 2 * (size_t)nh * (kt + 8) * 2 : 0);
 }
+
+#define AH_VARIANT_MMA 64
 
 // Whether attention_heads takes these sizes (else the caller uses attention_sink and head_mix):
 // returns the heads-per-thread variant (4 or 32), 0 if none fits.
-extern "C" int hb_attention_heads_variant(int n_heads, int n_kv_heads, int head_dim, int v_dim, int cache_dtype) {
+// `allow_mma` 0 keeps the tensor-core variant out (the tests compare the two).
+extern "C" int hb_attention_heads_variant(int n_heads, int n_kv_heads, int head_dim, int v_dim, int cache_dtype, int allow_mma) {
     const int elem = cache_dtype == HB_BF16 ? 2 : 4, ce = 16 / elem, kt = cache_dtype == HB_BF16 ? 32 : 16;
     if (n_heads <= 0 || n_kv_heads <= 0 || n_heads % n_kv_heads || head_dim % ce || v_dim % ce || v_dim % AH_CPT) return 0;
     const int nc = n_kv_heads * v_dim, col_threads = (nc + AH_CPT - 1) / AH_CPT;
+    if (allow_mma && cache_dtype == HB_BF16 && (n_heads == 16 || n_heads == 32) && nc % 16 == 0 && nc <= 1024
+        && ah_smem_bytes(n_heads, n_kv_heads, head_dim, v_dim, kt, elem, true) <= 200 * 1024)
+        return AH_VARIANT_MMA;
     if (col_threads > AH_THREADS) return 0;
-    if (ah_smem_bytes(n_heads, n_kv_heads, head_dim, v_dim, kt, elem) > 200 * 1024) return 0;
+    if (ah_smem_bytes(n_heads, n_kv_heads, head_dim, v_dim, kt, elem, false) > 200 * 1024) return 0;
     const int hg = min(AH_THREADS / col_threads, n_heads), hpt = (n_heads + hg - 1) / hg;
     return hpt <= 4 ? 4 : hpt <= 32 ? 32 : 0;
 }
 
-template <typename TQ, typename TC, typename TO, int HPT, int KT>
+// Whether a step of one split gets its output (heads mixed, normalised) from the block itself.
+extern "C" int hb_attention_heads_writes_output(int n_heads, int n_kv_heads, int head_dim, int v_dim, int cache_dtype, int allow_mma) {
+    const int variant = hb_attention_heads_variant(n_heads, n_kv_heads, head_dim, v_dim, cache_dtype, allow_mma);
+    if (variant == AH_VARIANT_MMA) return 1;
+    if (variant == 0) return 0;
+    const int col_threads = (n_kv_heads * v_dim + AH_CPT - 1) / AH_CPT;
+    return min(AH_THREADS / col_threads, n_heads) == 1 ? 1 : 0;
+}
+
+template <typename TQ, typename TC, typename TO, int HPT, int KT, bool MMA>
 static int ah_launch(dim3 grid, size_t smem, cudaStream_t s, const void* q, long long ldq, const void* k_cache, const void* v_cache,
                      const int* page_table, int pt_width, const int* tok_seq, const int* positions, float* partial, float* ml,
                      const float* mix, void* out, long long ldo, int ones, int nh, int nkv, int hd, int vd, float scale, int window,
                      int keep_first, int splits, int n_pages, int* status) {
     static bool done[HB_MAX_DEVICES];
     if (!done[hb_device_slot()]) {
-        cudaError_t e = cudaFuncSetAttribute(attention_heads_kernel<TQ, TC, TO, HPT, KT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        cudaError_t e = cudaFuncSetAttribute(attention_heads_kernel<TQ, TC, TO, HPT, KT, MMA>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
         if (e != cudaSuccess) return hb_fail("attention_heads: %s", cudaGetErrorString(e));
         done[hb_device_slot()] = true;
     }
-    hb_launch(attention_heads_kernel<TQ, TC, TO, HPT, KT>, dim3(grid), dim3(AH_THREADS), smem, s, (const TQ*)q, ldq, (const TC*)k_cache,
+    hb_launch(attention_heads_kernel<TQ, TC, TO, HPT, KT, MMA>, dim3(grid), dim3(AH_THREADS), smem, s, (const TQ*)q, ldq, (const TC*)k_cache,
               (const TC*)v_cache, page_table, pt_width, tok_seq, positions, partial, ml, mix, (TO*)out, ldo, ones, nh, nkv, hd, vd, scale,
               window, keep_first, splits, n_pages, status);
     return hb_check_launch("attention_heads");
@@ -554,26 +703,25 @@ extern "C" int hb_attention_heads(const void* q, int q_dtype, long long ldq, con
                                   const int* page_table, int pt_width, const int* tok_seq, const int* positions, float* partial,
                                   float* ml, const float* mix, void* out, long long ldo, int ones, int n_tokens, int n_heads,
                                   int n_kv_heads, int head_dim, int v_dim, float scale, int window, int keep_first, int splits,
-                                  int n_pages, int* status, void* stream) {
+                                  int n_pages, int allow_mma, int* status, void* stream) {
     if (n_tokens == 0) return 0;
-    const int variant = hb_attention_heads_variant(n_heads, n_kv_heads, head_dim, v_dim, cache_dtype);
+    const int variant = hb_attention_heads_variant(n_heads, n_kv_heads, head_dim, v_dim, cache_dtype, allow_mma);
     HB_REQUIRE(variant != 0, "attention_heads: these head sizes are not built");
     HB_REQUIRE(q_dtype == cache_dtype, "attention_heads: queries and cache must have one dtype");
     HB_REQUIRE(splits >= 1 && splits <= 65535 && window >= 0 && keep_first >= 0 && n_pages > 0, "attention_heads: bad sizes");
-    const int nc = n_kv_heads * v_dim, col_threads = (nc + AH_CPT - 1) / AH_CPT;
-    const bool whole = min(AH_THREADS / col_threads, n_heads) == 1;
+    const bool whole = hb_attention_heads_writes_output(n_heads, n_kv_heads, head_dim, v_dim, cache_dtype, allow_mma) != 0;
     HB_REQUIRE(out == nullptr || (splits == 1 && whole), "attention_heads: the block writes the output only with one split and every head in one thread");
     HB_REQUIRE(out != nullptr || (partial != nullptr && ml != nullptr), "attention_heads: no place for the partial results");
     const bool bf = cache_dtype == HB_BF16;
-    const size_t smem = ah_smem_bytes(n_heads, n_kv_heads, head_dim, v_dim, bf ? 32 : 16, bf ? 2 : 4);
+    const size_t smem = ah_smem_bytes(n_heads, n_kv_heads, head_dim, v_dim, bf ? 32 : 16, bf ? 2 : 4, variant == AH_VARIANT_MMA);
     dim3 grid(n_tokens, splits);
     cudaStream_t s = (cudaStream_t)stream;
-#define HB_AH(TQ, TO, HPT, KT)                                                                                                     \
-    return ah_launch<TQ, TQ, TO, HPT, KT>(grid, smem, s, q, ldq, k_cache, v_cache, page_table, pt_width, tok_seq, positions, partial, ml,  \
+#define HB_AH(TQ, TO, HPT, KT, MMA)                                                                                                \
+    return ah_launch<TQ, TQ, TO, HPT, KT, MMA>(grid, smem, s, q, ldq, k_cache, v_cache, page_table, pt_width, tok_seq, positions, partial, ml,  \
                                           mix, out, ldo, ones, n_heads, n_kv_heads, head_dim, v_dim, scale, window, keep_first, splits,  \
                                           n_pages, status)
-    if (bf) { if (variant == 4) HB_AH(bf16, bf16, 4, 32); else HB_AH(bf16, bf16, 32, 32); }
-    else { if (variant == 4) HB_AH(float, float, 4, 16); else HB_AH(float, float, 32, 16); }
+    if (bf) { if (variant == AH_VARIANT_MMA) HB_AH(bf16, bf16, 1, 32, true); else if (variant == 4) HB_AH(bf16, bf16, 4, 32, false); else HB_AH(bf16, bf16, 32, 32, false); }
+    else { if (variant == 4) HB_AH(float, float, 4, 16, false); else HB_AH(float, float, 32, 16, false); }
 #undef HB_AH
 }
 

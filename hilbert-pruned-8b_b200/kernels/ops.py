@@ -40,7 +40,8 @@ _SIGNATURES = {
                           _c_int, _c_int, _c_int, _c_float, _c_int, _c_int, _c_int, _c_int, _c_ptr, _c_ptr],
     "hb_head_mix": [_c_ptr, _c_ptr, _c_ptr, _c_int, _c_ll, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr],
     "hb_attention_heads": [_c_ptr, _c_int, _c_ll, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr,
-                           _c_ll, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_int, _c_int, _c_int, _c_ptr, _c_ptr],
+                           _c_ll, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr,
+                           _c_ptr],
     "hb_head_mix_splits": [_c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_ll, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr],
     "hb_mlstm_scan": [_c_ptr, _c_int, _c_ll, _c_ptr, _c_float, _c_float, _c_ptr, _c_ll, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int,
                       _c_int, _c_int, _c_ptr],
@@ -104,7 +105,8 @@ def load_library():
         lib.hb_gemm_tc2_resident_pairs.argtypes, lib.hb_gemm_tc2_resident_pairs.restype = [_c_int], _c_int
         for name in ("hb_attention_decode_supported", "hb_attention_prefill_supported", "hb_attention_prefill_tc_supported"):
             getattr(lib, name).argtypes, getattr(lib, name).restype = [_c_int, _c_int, _c_int], _c_int
-        lib.hb_attention_heads_variant.argtypes, lib.hb_attention_heads_variant.restype = [_c_int] * 5, _c_int
+        lib.hb_attention_heads_variant.argtypes, lib.hb_attention_heads_variant.restype = [_c_int] * 6, _c_int
+        lib.hb_attention_heads_writes_output.argtypes, lib.hb_attention_heads_writes_output.restype = [_c_int] * 6, _c_int
         lib.hb_attention_decode_ctas_per_sm.argtypes, lib.hb_attention_decode_ctas_per_sm.restype = [_c_int], _c_int
         lib.hb_attention_decode_scratch_floats.argtypes = [_c_int, _c_int, _c_int, _c_int]
         lib.hb_attention_decode_scratch_floats.restype = _c_ll
@@ -257,6 +259,9 @@ class Ops:
         self._splits_cache = {}
         self.use_tcgen05_attention = True   # head size 128 prefill on tcgen05 (else the mma.sync kernel)
         self.use_fast_attention = True  # tests switch this off to compare with the general kernel
+        # attention_heads: the weights-times-values product on the tensor cores (each 32-bit weight as two bfloat16
+        # terms) where the sizes allow; tests switch it off to compare with the FP32-pipe variant
+        self.use_mma_attention = True
         # Decode attention that rotates the new queries and key and appends to the cache itself
         # (no rotation kernel in front; the new key and value go into the owning split's copy of
         # their page in shared memory).  Inside a replayed graph at batch 8 / 8192 tokens it takes
@@ -506,19 +511,20 @@ class Ops:
 
     ATTENTION_HEADS_MAX_ROWS = 512      # tokens x key splits of a step that has fewer tokens than the device has SMs
 
-    @staticmethod
-    def attention_heads_whole(heads: int, kv_heads: int, v_dim: int) -> bool:
-        """Whether one thread of ``attention_heads`` holds every head of its value columns (the block can then mix the heads)."""
-        return min(512 // (-(-kv_heads * v_dim // 2)), heads) == 1
+    def attention_heads_whole(self, heads: int, kv_heads: int, head_dim: int, v_dim: int, dtype) -> bool:
+        """Whether a block of ``attention_heads`` holds every head of its value columns in one place (it can then mix the
+        heads and write the output itself when the keys are not split)."""
+        return bool(self.lib.hb_attention_heads_writes_output(heads, kv_heads, head_dim, v_dim, _DTYPE_CODE[dtype],
+                                                              1 if self.use_mma_attention else 0))
 
     def attention_heads_plan(self, tokens: int, heads: int, kv_heads: int, head_dim: int, v_dim: int, dtype, longest: int):
         """How ``attention_heads`` would run a step, or None when its kernel is not built for these sizes:
         ``(splits, writes_output)``.  Few tokens are cut over the keys (``longest``: the most keys a token sees) so that
         the device is busy; a step of many tokens with every head of a value column in one thread writes the mixed
         output itself."""
-        if not self.lib.hb_attention_heads_variant(heads, kv_heads, head_dim, v_dim, _DTYPE_CODE[dtype]):
+        if not self.lib.hb_attention_heads_variant(heads, kv_heads, head_dim, v_dim, _DTYPE_CODE[dtype], 1 if self.use_mma_attention else 0):
             return None
-        whole = self.attention_heads_whole(heads, kv_heads, v_dim)
+        whole = self.attention_heads_whole(heads, kv_heads, head_dim, v_dim, dtype)
         # the kernel that combines the splits keeps [heads, splits + v_dim] floats in 48 KB of shared memory
         most = (48 * 1024 // 4 - heads * v_dim) // heads
         if most < 1 and not whole:
@@ -550,7 +556,7 @@ class Ops:
                    self._f32_vec(mix, heads * heads, "head mix") if mix is not None else None,
                    out.data_ptr() if out is not None else None, _rows(out, "attention output") if out is not None else 0, ones,
                    T, heads, kv_heads, head_dim, v_dim, float(scale), int(window) if window else 0, int(keep_first), int(splits),
-                   cache.k.shape[0], self.status.data_ptr(), self._stream())
+                   cache.k.shape[0], 1 if self.use_mma_attention else 0, self.status.data_ptr(), self._stream())
         self.launches += 1
 
     def head_mix_splits(self, partial, ml, mix, out, heads: int, kv_heads: int, v_dim: int, splits: int, ones: int = 0) -> None:

@@ -136,7 +136,8 @@ class SinkAttention(Mixer):
                                     mix=self.talk_matrix, out=attn, ones=ones)
             else:
                 # tokens x splits at most: the same buffer for every step, a captured graph holds its address
-                rows = ops.ATTENTION_HEADS_MAX_ROWS if ops.attention_heads_whole(H, G, dv) else max(cap, ops.ATTENTION_HEADS_MAX_ROWS)
+                rows = (ops.ATTENTION_HEADS_MAX_ROWS if ops.attention_heads_whole(H, G, d, dv, self.ctx.dtype)
+                        else max(cap, ops.ATTENTION_HEADS_MAX_ROWS))
                 partial = ws.buffer("sink_attention.partial", (rows, H * G * dv), torch.float32)
                 ml = ws.buffer("sink_attention.ml", (rows, H * 2), torch.float32)
                 ops.attention_heads(q, H, G, d, dv, cache, step, self.scale, self.window, self.keep_first, splits,

@@ -54,7 +54,13 @@ WIDE = config(128, 300, 4, [
     with_mlp(mlstm(2, 32, 64, 10.0), None),
     with_mlp(attention(4, 2, 32, 64, 33, 7, 32, None), 128)], scale=0.5)
 
-CONFIGS = {"mixed": MIXED, "edges": EDGES, "recurrent": RECURRENT, "wide": WIDE}
+# sixteen heads: the sizes whose weights-times-values product runs on the tensor cores in bfloat16
+MANY_HEADS = config(128, 250, 2, [
+    with_mlp(attention(16, 4, 16, 32, 45, 2, 8, YARN), 160),
+    with_mlp(mlstm(4, 16, 32, 9.0), None),
+    with_mlp(attention(16, 4, 16, 32, 45, 2, 8, YARN), None)], scale=0.6)
+
+CONFIGS = {"mixed": MIXED, "edges": EDGES, "recurrent": RECURRENT, "wide": WIDE, "many_heads": MANY_HEADS}
 
 
 def draw_tensors(cfg, seed):

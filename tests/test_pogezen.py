@@ -16,7 +16,7 @@ from plain_pogezen import (PlainPogezen, causal_conv, dyt, mlstm_scan, rms_unit,
                            yarn_frequencies)
 
 DTYPES = ["float32", "bfloat16"]
-NAMES = ["mixed", "edges", "recurrent", "wide"]
+NAMES = ["mixed", "edges", "recurrent", "wide", "many_heads"]
 
 
 # --------------------------------------------------------------------------- helpers
@@ -316,7 +316,8 @@ def test_matrix_memory_in_portions_equals_the_scan(heads, d, dv):
 @pytest.mark.gpu
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("H,G,d,dv,size,keep,rot", [(4, 2, 16, 8, 70, 3, 8), (2, 2, 8, 24, 64, 0, 8), (3, 1, 32, 16, 129, 65, 0),
-                                                     (6, 3, 64, 40, 5, 1, 32), (8, 4, 32, 256, 100, 2, 16), (3, 1, 20, 12, 40, 3, 4)])
+                                                     (6, 3, 64, 40, 5, 1, 32), (8, 4, 32, 256, 100, 2, 16), (3, 1, 20, 12, 40, 3, 4),
+                                                     (16, 4, 32, 32, 70, 3, 16), (32, 8, 16, 24, 100, 2, 8), (32, 2, 64, 64, 33, 40, 32)])
 def test_attention_sees_exactly_the_window_and_the_first_tokens(H, G, d, dv, size, keep, rot, dtype):
     """A prompt of 300 tokens, then tokens one by one.  For some queries one key is made to stand
     out (its score dwarfs the others): the key just inside the window, just outside it, the last
@@ -381,10 +382,20 @@ def test_attention_sees_exactly_the_window_and_the_first_tokens(H, G, d, dv, siz
                 again = torch.empty_like(out)
                 ops.head_mix_splits(part, ml, talk.reshape(-1).cuda(), again, H, G, dv, splits, 8)
                 assert (again.float() - out.float()).abs().max().item() <= (1e-5 if dtype == torch.float32 else 2e-2) * max(1.0, out.float().abs().max().item())
-            if ops.attention_heads_whole(H, G, dv):
+            for mma in (True, False):       # the weights-times-values product on the tensor cores, and on the FP32 pipe
+                ops.use_mma_attention = mma
+                if ops.attention_heads_whole(H, G, d, dv, dtype):
+                    again = torch.empty_like(out)
+                    ops.attention_heads(qb, H, G, d, dv, view, step, scale, size, keep, 1, mix=talk.reshape(-1).cuda(), out=again, ones=8)
+                    assert (again.float() - out.float()).abs().max().item() <= (1e-5 if dtype == torch.float32 else 2e-2) * max(1.0, out.float().abs().max().item())
+                    assert torch.equal(again[:, H * dv:].float().cpu(), torch.tensor([1.0] + [0.0] * 7).expand(new, 8))
+                part = torch.full((new * H * 5 * G * dv,), float("nan"), device="cuda")
+                ml = torch.empty(new * H * 5 * 2, device="cuda")
+                ops.attention_heads(qb, H, G, d, dv, view, step, scale, size, keep, 5, partial=part, ml=ml)
                 again = torch.empty_like(out)
-                ops.attention_heads(qb, H, G, d, dv, view, step, scale, size, keep, 1, mix=talk.reshape(-1).cuda(), out=again, ones=8)
+                ops.head_mix_splits(part, ml, talk.reshape(-1).cuda(), again, H, G, dv, 5, 8)
                 assert (again.float() - out.float()).abs().max().item() <= (1e-5 if dtype == torch.float32 else 2e-2) * max(1.0, out.float().abs().max().item())
+            ops.use_mma_attention = True
         _commit(cache, seqs, [new])
     ops.check_errors()
     got = torch.cat(got).double()
@@ -537,7 +548,7 @@ def test_fused_norm_and_convolution_equal_the_two_kernels(models, name):
 
 @pytest.mark.gpu
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("name", ["mixed", "edges", "wide"])
+@pytest.mark.parametrize("name", ["mixed", "edges", "wide", "many_heads"])
 def test_attention_kernels_agree(models, name, dtype):
     """The kernel that serves all heads per block (with key splits in decode steps) against the general one."""
     require_gpu()
