@@ -727,20 +727,22 @@ extern "C" int hb_attention_heads(const void* q, int q_dtype, long long ldq, con
 
 // Combines key splits and mixes heads: out[t, h*vd + d] = sum_g mix[h, g] * (sum_s w_gs acc[t, g, s, c(h), d]) / (sum_s w_gs l_gs),
 // w_gs = exp(m_gs - max_s m_gs); mix null: the head's own.
+#define HM_COLS 32
 template <typename TO>
 __global__ void __launch_bounds__(256)
 head_mix_splits_kernel(const float* __restrict__ partial, const float* __restrict__ ml, const float* __restrict__ mix,
                        TO* __restrict__ out, long long ldo, int nh, int nkv, int vd, int splits, int ones) {
-    // one block per (token, value head c): first the splits of every head are combined for the columns of c
-    // (shared memory [nh][vd]), then the heads that use c mix them
+    // one block per (token, value head c, run of HM_COLS columns of c): first the splits of every head are combined
+    // for these columns (shared memory [nh][HM_COLS]), then the heads that use c mix them
     pdl_trigger();
     pdl_wait();
     partial = pdl_fresh(partial);
     ml = pdl_fresh(ml);
     extern __shared__ float hm_smem[];
     float* wts = hm_smem;                               // [nh][splits]: w_gs / (sum_s w_gs l_gs)
-    float* comb = hm_smem + nh * splits;                // [nh][vd]
+    float* comb = hm_smem + nh * splits;                // [nh][HM_COLS]
     const int t = blockIdx.x, c = blockIdx.y, NC = nkv * vd, group = nh / nkv;
+    const int d_begin = blockIdx.z * HM_COLS, dw = min(HM_COLS, vd - d_begin);
     for (int g = threadIdx.x; g < nh; g += blockDim.x) {
         const float* r = ml + ((size_t)t * nh + g) * splits * 2;
         float M = -INFINITY, den = 0.0f;
@@ -749,27 +751,27 @@ head_mix_splits_kernel(const float* __restrict__ partial, const float* __restric
         for (int s = 0; s < splits; s++) wts[g * splits + s] = den > 0.0f ? (r[2 * s] == -INFINITY ? 0.0f : expf(r[2 * s] - M)) / den : 0.0f;
     }
     __syncthreads();
-    const float* pr = partial + (size_t)t * nh * splits * NC + (size_t)c * vd;
-    for (int e = threadIdx.x; e < nh * vd; e += blockDim.x) {
-        const int g = e / vd, d = e - g * vd;
+    const float* pr = partial + (size_t)t * nh * splits * NC + (size_t)c * vd + d_begin;
+    for (int e = threadIdx.x; e < nh * dw; e += blockDim.x) {
+        const int g = e / dw, d = e - g * dw;
         float v = 0.0f;
         for (int s = 0; s < splits; s++) v = fmaf(wts[g * splits + s], pr[((size_t)g * splits + s) * NC + d], v);
-        comb[e] = v;
+        comb[g * HM_COLS + d] = v;
     }
     __syncthreads();
     TO* o = out + (size_t)t * ldo;
-    for (int e = threadIdx.x; e < group * vd; e += blockDim.x) {
-        const int h = c * group + e / vd, d = e % vd;
+    for (int e = threadIdx.x; e < group * dw; e += blockDim.x) {
+        const int h = c * group + e / dw, d = e % dw;
         float a;
         if (mix != nullptr) {
             a = 0.0f;
-            for (int g = 0; g < nh; g++) a = fmaf(mix[h * nh + g], comb[g * vd + d], a);
+            for (int g = 0; g < nh; g++) a = fmaf(mix[h * nh + g], comb[g * HM_COLS + d], a);
         } else {
-            a = comb[h * vd + d];
+            a = comb[h * HM_COLS + d];
         }
-        o[h * vd + d] = from_f32<TO>(a);
+        o[h * vd + d_begin + d] = from_f32<TO>(a);
     }
-    if (c == 0)
+    if (c == 0 && blockIdx.z == 0)
         for (int e = threadIdx.x; e < ones; e += blockDim.x) o[nh * vd + e] = from_f32<TO>(e == 0 ? 1.0f : 0.0f);
 }
 
@@ -778,13 +780,13 @@ extern "C" int hb_head_mix_splits(const float* partial, const float* ml, const f
     if (n_tokens == 0) return 0;
     HB_REQUIRE(n_tokens > 0 && n_heads > 0 && n_kv_heads > 0 && v_dim > 0 && ones >= 0 && splits >= 1, "head_mix: bad sizes");
     HB_REQUIRE(ldo >= (long long)n_heads * v_dim + ones, "head_mix: output rows are too short");
-    const size_t smem = ((size_t)n_heads * splits + (size_t)n_heads * v_dim) * sizeof(float);
+    const size_t smem = ((size_t)n_heads * splits + (size_t)n_heads * HM_COLS) * sizeof(float);
     HB_REQUIRE(smem <= 48 * 1024 && n_kv_heads <= 65535, "head_mix: too many heads times (splits + value size)");
     cudaStream_t s = (cudaStream_t)stream;
     if (out_dtype == HB_BF16)
-        hb_launch(head_mix_splits_kernel<bf16>, dim3(n_tokens, n_kv_heads), dim3(256), smem, s, partial, ml, mix, (bf16*)out, ldo, n_heads, n_kv_heads, v_dim, splits, ones);
+        hb_launch(head_mix_splits_kernel<bf16>, dim3(n_tokens, n_kv_heads, (v_dim + HM_COLS - 1) / HM_COLS), dim3(256), smem, s, partial, ml, mix, (bf16*)out, ldo, n_heads, n_kv_heads, v_dim, splits, ones);
     else if (out_dtype == HB_F32)
-        hb_launch(head_mix_splits_kernel<float>, dim3(n_tokens, n_kv_heads), dim3(256), smem, s, partial, ml, mix, (float*)out, ldo, n_heads, n_kv_heads, v_dim, splits, ones);
+        hb_launch(head_mix_splits_kernel<float>, dim3(n_tokens, n_kv_heads, (v_dim + HM_COLS - 1) / HM_COLS), dim3(256), smem, s, partial, ml, mix, (float*)out, ldo, n_heads, n_kv_heads, v_dim, splits, ones);
     else return hb_fail("head_mix: unsupported output dtype %d", out_dtype);
     return hb_check_launch("head_mix_splits");
 }

@@ -525,8 +525,8 @@ class Ops:
         if not self.lib.hb_attention_heads_variant(heads, kv_heads, head_dim, v_dim, _DTYPE_CODE[dtype], 1 if self.use_mma_attention else 0):
             return None
         whole = self.attention_heads_whole(heads, kv_heads, head_dim, v_dim, dtype)
-        # the kernel that combines the splits keeps [heads, splits + v_dim] floats in 48 KB of shared memory
-        most = (48 * 1024 // 4 - heads * v_dim) // heads
+        # the kernel that combines the splits keeps [heads, splits + 32] floats in 48 KB of shared memory
+        most = (48 * 1024 // 4 - heads * 32) // heads
         if most < 1 and not whole:
             return None
         splits = 1
