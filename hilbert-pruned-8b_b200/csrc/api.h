@@ -128,6 +128,13 @@ int hb_attention_heads(const void* q, int q_dtype, long long ldq, const void* k_
                        void* stream);
 int hb_head_mix_splits(const float* partial, const float* ml, const float* mix, void* out, int out_dtype, long long ldo, int n_tokens,
                        int n_heads, int n_kv_heads, int v_dim, int splits, int ones, void* stream);
+// Flash-style on the tensor cores for steps of many tokens (bfloat16, head sizes 64 or 128); out float32
+// [tokens][heads][n_val][v_dim], n_val = kv heads (every value head) or 1 (the head's own); see attention_sink_prefill.cu.
+int hb_attention_sink_prefill_supported(int n_heads, int n_kv_heads, int head_dim, int v_dim);
+int hb_attention_sink_prefill(const void* q, long long q_stride, const void* k_cache, const void* v_cache, const int* page_table,
+                              int pt_width, const int* seq_start, const int* seq_pos0, float* out, int n_seqs, int q_blocks,
+                              int n_heads, int n_kv_heads, int head_dim, int v_dim, int n_val, float scale, int window,
+                              int keep_first, int n_pages, int* status, void* stream);
 // proj rows: [q heads*d | k heads*d | v heads*dv | gate heads*dv | z_i heads | z_f heads]; state per slot:
 // S [heads][d][dv], n [heads][d], m [heads]; out [tokens][heads*dv] float32
 int hb_mlstm_scan(const void* proj, int proj_dtype, long long ldp, const float* gate_bias, float cap, float q_scale, float* state,

@@ -42,6 +42,8 @@ _SIGNATURES = {
     "hb_attention_heads": [_c_ptr, _c_int, _c_ll, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr,
                            _c_ll, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr,
                            _c_ptr],
+    "hb_attention_sink_prefill": [_c_ptr, _c_ll, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int,
+                                  _c_int, _c_int, _c_int, _c_float, _c_int, _c_int, _c_int, _c_ptr, _c_ptr],
     "hb_head_mix_splits": [_c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_ll, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr],
     "hb_mlstm_scan": [_c_ptr, _c_int, _c_ll, _c_ptr, _c_float, _c_float, _c_ptr, _c_ll, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int,
                       _c_int, _c_int, _c_ptr],
@@ -105,6 +107,7 @@ def load_library():
         lib.hb_gemm_tc2_resident_pairs.argtypes, lib.hb_gemm_tc2_resident_pairs.restype = [_c_int], _c_int
         for name in ("hb_attention_decode_supported", "hb_attention_prefill_supported", "hb_attention_prefill_tc_supported"):
             getattr(lib, name).argtypes, getattr(lib, name).restype = [_c_int, _c_int, _c_int], _c_int
+        lib.hb_attention_sink_prefill_supported.argtypes, lib.hb_attention_sink_prefill_supported.restype = [_c_int] * 4, _c_int
         lib.hb_attention_heads_variant.argtypes, lib.hb_attention_heads_variant.restype = [_c_int] * 6, _c_int
         lib.hb_attention_heads_writes_output.argtypes, lib.hb_attention_heads_writes_output.restype = [_c_int] * 6, _c_int
         lib.hb_attention_decode_ctas_per_sm.argtypes, lib.hb_attention_decode_ctas_per_sm.restype = [_c_int], _c_int
@@ -262,6 +265,7 @@ class Ops:
         # attention_heads: the weights-times-values product on the tensor cores (each 32-bit weight as two bfloat16
         # terms) where the sizes allow; tests switch it off to compare with the FP32-pipe variant
         self.use_mma_attention = True
+        self.use_flash_sink_attention = True    # steps of many tokens: attention_sink_prefill where it is built
         # Decode attention that rotates the new queries and key and appends to the cache itself
         # (no rotation kernel in front; the new key and value go into the owning split's copy of
         # their page in shared memory).  Inside a replayed graph at batch 8 / 8192 tokens it takes
@@ -507,6 +511,36 @@ class Ops:
             raise KernelError("head_mix: shapes do not agree")
         self._call("hb_head_mix", partial.data_ptr(), self._f32_vec(mix, heads * heads, "head mix") if mix is not None else None,
                    out.data_ptr(), _code(out), _rows(out, "head_mix output"), T, heads, kv_heads, v_dim, n_val, ones, self._stream())
+        self.launches += 1
+
+    SINK_PREFILL_FROM = 16          # steps whose longest portion has at least so many tokens run the flash-style kernel
+
+    def attention_sink_prefill_wanted(self, step, heads: int, kv_heads: int, head_dim: int, v_dim: int, dtype) -> bool:
+        """Whether ``attention_sink_prefill`` takes this step: bfloat16, head sizes it is built for, a portion of
+        ``SINK_PREFILL_FROM`` tokens or more (64 query tokens share a block; fewer tokens are better cut over the keys)."""
+        return bool(self.use_flash_sink_attention and dtype == torch.bfloat16 and not step.is_decode
+                    and step.max_new >= self.SINK_PREFILL_FROM
+                    and self.lib.hb_attention_sink_prefill_supported(heads, kv_heads, head_dim, v_dim)
+                    and sum((n + 63) // 64 for n in step.host_new) <= 65535)
+
+    def attention_sink_prefill(self, q, heads: int, kv_heads: int, head_dim: int, v_dim: int, cache, step, partial, scale: float,
+                               window: Optional[int], keep_first: int, all_values: bool) -> None:
+        """``attention_sink`` on the tensor cores, 64 query tokens of a sequence per block: ``partial`` float32
+        ``[tokens, heads, kv_heads if all_values else 1, v_dim]``, normalised."""
+        self._dev(q, cache.k, cache.v, partial)
+        T = q.shape[0]
+        n_val = kv_heads if all_values else 1
+        if q.dtype != torch.bfloat16 or cache.k.dtype != torch.bfloat16 or partial.dtype != torch.float32 or not partial.is_contiguous() \
+                or partial.numel() != T * heads * n_val * v_dim:
+            raise KernelError("attention_sink_prefill: bfloat16 queries and cache, float32 [tokens, heads, value heads, v_dim] expected")
+        if tuple(cache.k.shape[1:]) != (kv_heads, 64, head_dim) or tuple(cache.v.shape[1:]) != (kv_heads, 64, v_dim):
+            raise KernelError("attention_sink_prefill: cache layer does not match the heads")
+        pt = step.page_tables[cache.group]
+        q_blocks = sum((n + 63) // 64 for n in step.host_new)
+        self._call("hb_attention_sink_prefill", q.data_ptr(), _rows(q, "queries"), cache.k.data_ptr(), cache.v.data_ptr(), pt.data_ptr(),
+                   pt.shape[1], step.seq_start.data_ptr(), step.seq_pos0.data_ptr(), partial.data_ptr(), step.num_seqs, q_blocks,
+                   heads, kv_heads, head_dim, v_dim, n_val, float(scale), int(window) if window else 0, int(keep_first),
+                   cache.k.shape[0], self.status.data_ptr(), self._stream())
         self.launches += 1
 
     ATTENTION_HEADS_MAX_ROWS = 512      # tokens x key splits of a step that has fewer tokens than the device has SMs

@@ -128,7 +128,14 @@ class SinkAttention(Mixer):
         attn = ws.buffer("sink_attention.out", (cap, self.out_width + ones), self.ctx.dtype)[:T]
         longest = step.max_len if self.window is None else min(step.max_len, self.window + self.keep_first)
         plan = ops.attention_heads_plan(T, H, G, d, dv, self.ctx.dtype, longest) if self.use_heads_kernel else None
-        if plan is not None:
+        if self.use_heads_kernel and ops.attention_sink_prefill_wanted(step, H, G, d, dv, self.ctx.dtype):
+            # many tokens: 64 query tokens of a sequence share a block's keys and values (flash-style, tensor cores)
+            all_values = self.talk and G > 1
+            n_val = G if all_values else 1
+            partial = ws.buffer("sink_attention.partial_general", (cap, H * n_val * dv), torch.float32)[:T]
+            ops.attention_sink_prefill(q, H, G, d, dv, cache, step, partial, self.scale, self.window, self.keep_first, all_values)
+            ops.head_mix(partial, self.talk_matrix, attn, H, G, dv, n_val, ones)
+        elif plan is not None:
             # one block per (token, key split) serves all heads; it mixes the heads itself when it can
             splits, writes_output = plan
             if writes_output:

@@ -60,7 +60,14 @@ MANY_HEADS = config(128, 250, 2, [
     with_mlp(mlstm(4, 16, 32, 9.0), None),
     with_mlp(attention(16, 4, 16, 32, 45, 2, 8, YARN), None)], scale=0.6)
 
-CONFIGS = {"mixed": MIXED, "edges": EDGES, "recurrent": RECURRENT, "wide": WIDE, "many_heads": MANY_HEADS}
+# head sizes of 64 and 128: the flash-style kernel for prompts in bfloat16 (kept tokens beyond a page, windows of odd sizes)
+BIG_HEADS = config(128, 220, 3, [
+    with_mlp(attention(4, 2, 64, 64, 70, 3, 32, YARN), 160),
+    with_mlp(mlstm(2, 16, 32, 9.0), None),
+    with_mlp(attention(2, 1, 128, 64, 97, 66, 64, None, v_mix=False), None),
+    with_mlp(attention(4, 2, 64, 64, 1000, 0, 16, YARN), 96)], scale=0.6)
+
+CONFIGS = {"big_heads": BIG_HEADS, "mixed": MIXED, "edges": EDGES, "recurrent": RECURRENT, "wide": WIDE, "many_heads": MANY_HEADS}
 
 
 def draw_tensors(cfg, seed):

@@ -16,7 +16,7 @@ from plain_pogezen import (PlainPogezen, causal_conv, dyt, mlstm_scan, rms_unit,
                            yarn_frequencies)
 
 DTYPES = ["float32", "bfloat16"]
-NAMES = ["mixed", "edges", "recurrent", "wide", "many_heads"]
+NAMES = ["mixed", "edges", "recurrent", "wide", "many_heads", "big_heads"]
 
 
 # --------------------------------------------------------------------------- helpers
@@ -317,7 +317,8 @@ def test_matrix_memory_in_portions_equals_the_scan(heads, d, dv):
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("H,G,d,dv,size,keep,rot", [(4, 2, 16, 8, 70, 3, 8), (2, 2, 8, 24, 64, 0, 8), (3, 1, 32, 16, 129, 65, 0),
                                                      (6, 3, 64, 40, 5, 1, 32), (8, 4, 32, 256, 100, 2, 16), (3, 1, 20, 12, 40, 3, 4),
-                                                     (16, 4, 32, 32, 70, 3, 16), (32, 8, 16, 24, 100, 2, 8), (32, 2, 64, 64, 33, 40, 32)])
+                                                     (16, 4, 32, 32, 70, 3, 16), (32, 8, 16, 24, 100, 2, 8), (32, 2, 64, 64, 33, 40, 32),
+                                                     (4, 2, 64, 128, 70, 3, 32), (3, 1, 128, 64, 130, 65, 0), (8, 4, 128, 128, 64, 0, 64)])
 def test_attention_sees_exactly_the_window_and_the_first_tokens(H, G, d, dv, size, keep, rot, dtype):
     """A prompt of 300 tokens, then tokens one by one.  For some queries one key is made to stand
     out (its score dwarfs the others): the key just inside the window, just outside it, the last
@@ -373,6 +374,13 @@ def test_attention_sees_exactly_the_window_and_the_first_tokens(H, G, d, dv, siz
         ops.head_mix(partial, talk.reshape(-1).cuda(), out, H, G, dv, G, 8)
         assert torch.equal(out[:, H * dv:].float().cpu(), torch.tensor([1.0] + [0.0] * 7).expand(new, 8))
         got.append(out[:, : H * dv].float().cpu())
+        # the flash-style kernel for steps of many tokens (it takes any step; here also the single tokens)
+        if dtype == torch.bfloat16 and ops.lib.hb_attention_sink_prefill_supported(H, G, d, dv):
+            flash = torch.full((new * H * G * dv,), float("nan"), device="cuda")
+            ops.attention_sink_prefill(qb, H, G, d, dv, view, step, flash, scale, size, keep, True)
+            again = torch.empty_like(out)
+            ops.head_mix(flash, talk.reshape(-1).cuda(), again, H, G, dv, G, 8)
+            assert (again.float() - out.float()).abs().max().item() <= 2e-2 * max(1.0, out.float().abs().max().item())
         # the kernel that serves all heads of a token in one block: key splits combined afterwards, or the output at once
         if ops.attention_heads_plan(new, H, G, d, dv, dtype, 10 ** 6) is not None:
             for splits in (1, 3, 8):
@@ -548,7 +556,7 @@ def test_fused_norm_and_convolution_equal_the_two_kernels(models, name):
 
 @pytest.mark.gpu
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("name", ["mixed", "edges", "wide", "many_heads"])
+@pytest.mark.parametrize("name", ["mixed", "edges", "wide", "many_heads", "big_heads"])
 def test_attention_kernels_agree(models, name, dtype):
     """The kernel that serves all heads per block (with key splits in decode steps) against the general one."""
     require_gpu()
