@@ -725,6 +725,7 @@ extern "C" int hb_attention_heads(const void* q, int q_dtype, long long ldq, con
 #undef HB_AH
 }
 
+// ml null: one split whose sums are normalised already (the results of attention_sink_prefill for every value head).
 // Combines key splits and mixes heads: out[t, h*vd + d] = sum_g mix[h, g] * (sum_s w_gs acc[t, g, s, c(h), d]) / (sum_s w_gs l_gs),
 // w_gs = exp(m_gs - max_s m_gs); mix null: the head's own.
 #define HM_COLS 32
@@ -744,6 +745,10 @@ head_mix_splits_kernel(const float* __restrict__ partial, const float* __restric
     const int t = blockIdx.x, c = blockIdx.y, NC = nkv * vd, group = nh / nkv;
     const int d_begin = blockIdx.z * HM_COLS, dw = min(HM_COLS, vd - d_begin);
     for (int g = threadIdx.x; g < nh; g += blockDim.x) {
+        if (ml == nullptr) {                            // one split, already normalised
+            wts[g * splits] = 1.0f;
+            continue;
+        }
         const float* r = ml + ((size_t)t * nh + g) * splits * 2;
         float M = -INFINITY, den = 0.0f;
         for (int s = 0; s < splits; s++) M = fmaxf(M, r[2 * s]);
@@ -780,6 +785,7 @@ extern "C" int hb_head_mix_splits(const float* partial, const float* ml, const f
     if (n_tokens == 0) return 0;
     HB_REQUIRE(n_tokens > 0 && n_heads > 0 && n_kv_heads > 0 && v_dim > 0 && ones >= 0 && splits >= 1, "head_mix: bad sizes");
     HB_REQUIRE(ldo >= (long long)n_heads * v_dim + ones, "head_mix: output rows are too short");
+    HB_REQUIRE(ml != nullptr || splits == 1, "head_mix: several splits need their maxima and sums");
     const size_t smem = ((size_t)n_heads * splits + (size_t)n_heads * HM_COLS) * sizeof(float);
     HB_REQUIRE(smem <= 48 * 1024 && n_kv_heads <= 65535, "head_mix: too many heads times (splits + value size)");
     cudaStream_t s = (cudaStream_t)stream;

@@ -594,12 +594,13 @@ class Ops:
         self.launches += 1
 
     def head_mix_splits(self, partial, ml, mix, out, heads: int, kv_heads: int, v_dim: int, splits: int, ones: int = 0) -> None:
-        """Combines the key splits of ``attention_heads`` and mixes the heads (``mix`` None: each head its own)."""
+        """Combines the key splits of ``attention_heads`` and mixes the heads (``mix`` None: each head its own).  ``ml`` None:
+        one split, normalised already (``partial`` is then ``[tokens, heads, kv_heads, v_dim]``)."""
         self._dev(partial, ml, mix, out)
         T = out.shape[0]
         if out.shape[1] != heads * v_dim + ones:
             raise KernelError("head_mix_splits: shapes do not agree")
-        self._call("hb_head_mix_splits", partial.data_ptr(), ml.data_ptr(),
+        self._call("hb_head_mix_splits", partial.data_ptr(), ml.data_ptr() if ml is not None else None,
                    self._f32_vec(mix, heads * heads, "head mix") if mix is not None else None, out.data_ptr(), _code(out),
                    _rows(out, "head_mix output"), T, heads, kv_heads, v_dim, splits, ones, self._stream())
         self.launches += 1

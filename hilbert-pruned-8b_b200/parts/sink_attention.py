@@ -134,7 +134,10 @@ class SinkAttention(Mixer):
             n_val = G if all_values else 1
             partial = ws.buffer("sink_attention.partial_general", (cap, H * n_val * dv), torch.float32)[:T]
             ops.attention_sink_prefill(q, H, G, d, dv, cache, step, partial, self.scale, self.window, self.keep_first, all_values)
-            ops.head_mix(partial, self.talk_matrix, attn, H, G, dv, n_val, ones)
+            if n_val == G:
+                ops.head_mix_splits(partial, None, self.talk_matrix, attn, H, G, dv, 1, ones)
+            else:
+                ops.head_mix(partial, None, attn, H, G, dv, n_val, ones)
         elif plan is not None:
             # one block per (token, key split) serves all heads; it mixes the heads itself when it can
             splits, writes_output = plan
