@@ -1,4 +1,4 @@
-"""A small generation library for the Llama 3 dense decoder on one NVIDIA B200.
+"""A small generation library for one NVIDIA B200: the Llama 3 dense decoder and the Pogezen decoder.
 
 Everything between a request's token ids and its next token: typed configuration and
 architecture registry, weights by tensor name, layers put together from parts, a paged
