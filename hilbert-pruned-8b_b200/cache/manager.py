@@ -13,6 +13,10 @@ fixed-size state arrays for its other layer kind (cleanroom-transformer/src/cpu_
 310-337; transformer.h:307-318); rewinding is a position reset (cpu_backend.c:279-292).
 Batches, slots and paging are this library's own.
 
+A plan entry may own several groups (its mixer's ``cache_need()`` is then a tuple): ``view`` gives
+a view per need.  A need with ``stride`` s keeps one entry per whole run of s tokens; its group's
+pages hold 64 such entries each and a sequence of n tokens holds ``n // s`` of them.
+
 Per-sequence state of fixed size lives in ``state[entry]: [slots, *shape]``; a sequence's
 slot is zeroed when the sequence opens.  The Llama decoder has no such state: the area
 exists, with zero entries.
@@ -68,6 +72,10 @@ class CacheGroup:
     def __init__(self, need: CacheNeed, entries: List[int], num_pages: int, device, dtype,
                  allocate: bool = True):
         self.need = need
+        self.stride = max(1, int(need.stride))
+        if need.store_f32:
+            dtype = torch.float32
+        self.dtype = dtype
         self.entries = list(entries)
         self.index_of = {e: i for i, e in enumerate(entries)}
         self.pool = IndexPool(num_pages, "page")
@@ -82,8 +90,15 @@ class CacheGroup:
         else:
             self.k = self.v = None
 
+    def pages_for(self, tokens: int) -> int:
+        """Pages a sequence of ``tokens`` tokens holds in this group."""
+        return pages_for(tokens // self.stride)
+
     def bytes_per_token(self, element_size: int) -> int:
-        return len(self.entries) * self.need.num_kv_heads * (self.need.head_dim + self.need.value_dim) * element_size
+        if self.need.store_f32:
+            element_size = 4
+        per_entry = len(self.entries) * self.need.num_kv_heads * (self.need.head_dim + self.need.value_dim) * element_size
+        return -(-per_entry // self.stride)
 
 
 class CacheManager:
@@ -97,15 +112,27 @@ class CacheManager:
         self.num_pages = pages_for(max_tokens)
         self.max_sequences = max_sequences if max_sequences is not None else min(self.num_pages, 1024)
         by_need: Dict[CacheNeed, List[int]] = {}
+        self._several: Dict[int, bool] = {}
         for entry in sorted(cache_needs):
-            by_need.setdefault(cache_needs[entry], []).append(entry)
+            needs = cache_needs[entry]
+            self._several[entry] = isinstance(needs, (tuple, list))
+            for need in (needs if self._several[entry] else (needs,)):
+                by_need.setdefault(need, []).append(entry)
+
+        def group_pages(need: CacheNeed) -> int:
+            # a strided group holds tokens // stride entries per sequence: every live sequence may leave a page partly used
+            if need.stride <= 1:
+                return self.num_pages
+            return min(self.num_pages, pages_for(max_tokens // need.stride) + self.max_sequences)
+
         self.groups: List[CacheGroup] = [
-            CacheGroup(need, entries, self.num_pages, device, dtype, allocate) for need, entries in by_need.items()]
+            CacheGroup(need, entries, group_pages(need), device, dtype, allocate) for need, entries in by_need.items()]
         self._windowed = any(g.need.window is not None for g in self.groups)
-        self._group_of_entry: Dict[int, int] = {}
-        for gi, g in enumerate(self.groups):
-            for e in g.entries:
-                self._group_of_entry[e] = gi
+        self._groups_of_entry: Dict[int, List[int]] = {}
+        for entry in sorted(cache_needs):
+            needs = cache_needs[entry]
+            for need in (needs if self._several[entry] else (needs,)):
+                self._groups_of_entry.setdefault(entry, []).append(list(by_need).index(need))
         self.slots = IndexPool(self.max_sequences, "sequence slot")
         self.state: Dict[int, torch.Tensor] = {}
         self.state_needs = dict(state_needs)
@@ -145,7 +172,7 @@ class CacheManager:
         for seq, new_len in seqs_and_lengths:
             for gi, g in enumerate(self.groups):
                 have = len(seq.pages[gi])
-                need[gi] += max(0, pages_for(new_len) - have)
+                need[gi] += max(0, g.pages_for(new_len) - have)
         return need
 
     def check_room(self, seqs_and_lengths: List[Tuple[Sequence, int]]) -> None:
@@ -180,7 +207,7 @@ class CacheManager:
                     f"{g.pool.num_free} of {g.pool.size} are free (max_tokens {self.max_tokens})")
         for seq, new_len in seqs_and_lengths:
             for gi, g in enumerate(self.groups):
-                extra = pages_for(new_len) - len(seq.pages[gi])
+                extra = g.pages_for(new_len) - len(seq.pages[gi])
                 if extra > 0:
                     seq.pages[gi].extend(g.pool.alloc(extra))
                     seq.pages_version += 1
@@ -220,13 +247,14 @@ class CacheManager:
             raise ValueError(f"cache: sequence {seq.seq_id} is closed")
         if length > seq.length or length < 0:
             raise ValueError("cache: truncate needs 0 <= length <= current length")
-        keep = pages_for(length)
         for gi, g in enumerate(self.groups):
             w = g.need.window
+            keep = g.pages_for(length)
             if w is not None and (any(p is None for p in seq.pages[gi][max(0, (length - w)) // PAGE_TOKENS:keep])
                                   or any(p is None for p in seq.pages[gi][:min(keep, pages_for(g.need.keep_first))])):
                 raise ValueError("cache: pages inside the rewound window were already given back")
         for gi, g in enumerate(self.groups):
+            keep = g.pages_for(length)
             tail = seq.pages[gi][keep:]
             g.pool.free([p for p in tail if p is not None])
             del seq.pages[gi][keep:]
@@ -252,15 +280,20 @@ class CacheManager:
 
     # ------------------------------------------------------------------ views
     def group_of(self, entry: int) -> int:
-        return self._group_of_entry[entry]
+        return self._groups_of_entry[entry][0]
 
-    def view(self, entry: int) -> Optional[LayerCache]:
-        gi = self._group_of_entry.get(entry)
-        if gi is None:
+    def view(self, entry: int):
+        """The entry's storage: a ``LayerCache``, a tuple of them for a mixer that asked for several
+        needs (in the order it named them), None for an entry that keeps no keys and values."""
+        gis = self._groups_of_entry.get(entry)
+        if gis is None:
             return None
-        g = self.groups[gi]
-        i = g.index_of[entry]
-        return LayerCache(g.k[i], g.v[i], gi, g.need.window)
+        views = []
+        for gi in gis:
+            g = self.groups[gi]
+            i = g.index_of[entry]
+            views.append(LayerCache(g.k[i], g.v[i], gi, g.need.window))
+        return tuple(views) if self._several[entry] else views[0]
 
     def state_view(self, entry: int) -> Optional[torch.Tensor]:
         return self.state.get(entry)
@@ -275,3 +308,6 @@ class CacheManager:
     def bytes_per_token(self) -> int:
         es = torch.empty((), dtype=self.dtype).element_size()
         return sum(g.bytes_per_token(es) for g in self.groups)
+
+    def pages_of_group(self, gi: int) -> int:
+        return self.groups[gi].pool.size

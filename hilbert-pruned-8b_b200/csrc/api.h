@@ -155,6 +155,57 @@ int hb_sample(const float* logits, long long stride, const float* temperature, c
               const long long* request_ids, const long long* steps, int* out, int n_rows, int vocab, int* status,
               void* stream);
 
+// A norm on a sublayer's output on its way into the residual stream: x += rmsnorm(y) * (offset + w); with w2 and h
+// also h = rmsnorm(x) * (offset2 + w2) for the next sublayer (post_norm.cu).  out = sa a + sb b over n floats.
+int hb_rmsnorm_add(const float* y, long long ldy, const float* w, float eps, float offset, float* x, long long ldx,
+                   const float* w2, float eps2, float offset2, void* h, int h_dtype, long long ldh, int n_rows, int n, void* stream);
+int hb_scaled_sum(const float* a, float sa, const float* b, float sb, float* out, long long n, void* stream);
+// Window + pooled-block attention with sigmoid weights (attention_pool.cu).  proj rows: [q heads*d | k kv*d | v kv*dv | ...] float32.
+int hb_qk_norm_append(const float* proj, long long ldp, const float* q_weight, const float* k_weight, float eps, void* q_out,
+                      int q_dtype, long long ldq, void* k_cache, void* v_cache, int cache_dtype, const int* page_table, int pt_width,
+                      const int* tok_seq, const int* positions, int n_tokens, int n_heads, int n_kv_heads, int head_dim, int v_dim,
+                      int n_pages, int append, int* status, void* stream);
+int hb_pool_blocks(const void* k_cache, const void* v_cache, int cache_dtype, float* pk_cache, float* pv_cache, const int* pt_tok,
+                   const int* pt_pool, int pt_width, const int* seq_pos0, const int* seq_len, int n_seqs, int max_new, int pool,
+                   int n_kv_heads, int head_dim, int v_dim, int n_pages_tok, int n_pages_pool, int* status, void* stream);
+int hb_attention_pool_supported(int head_dim, int v_dim);
+// q_tiles: sum over the sequences of ceil(new tokens / 16); gate (float32, may be null) multiplies the result by its sigmoid;
+// splits > 1: the keys are cut into ranges whose sums go to partial [splits][tokens][heads * v_dim] and are added by a second kernel
+int hb_attention_pool(const void* q, int q_dtype, long long ldq, const void* k_cache, const void* v_cache, int cache_dtype,
+                      const float* pk_cache, const float* pv_cache, const int* pt_tok, const int* pt_pool, int pt_width,
+                      const int* seq_start, const int* seq_pos0, int n_seqs, int q_tiles, const float* head_bias, const float* gate,
+                      long long ldg, void* out, int out_dtype, long long ldo, float* partial, int n_tokens, int n_heads, int n_kv_heads,
+                      int head_dim, int v_dim, float scale, int window, int pool, int n_pages_tok, int n_pages_pool, int splits,
+                      int* status, void* stream);
+// Matrix memory with a fixed decay per head (decay_memory.cu).  proj rows: [q heads*d | k heads*d | v heads*dv | ...] float32;
+// state per slot: S [heads][d][dv]; out [tokens][heads*dv] float32; act 1: silu on q, k and v
+int hb_decay_memory(const float* proj, long long ldp, const float* decay, float* state, long long state_stride, const int* state_slots,
+                    const int* seq_start, float* out, long long ldo, int n_seqs, int n_heads, int d, int dv, int act, void* stream);
+int hb_gated_norm(const float* o, long long ldi, const float* gate, long long ldg, const float* w, float eps, float out_scale, void* out,
+                  int out_dtype, long long ldo, int n_rows, int n, void* stream);
+// Short causal convolution with bias, activation and state; selective state-space scan (selective_scan.cu)
+int hb_conv_act(const float* x, long long ldx, const float* conv_w, const float* conv_b, int taps, float* state, long long state_stride,
+                const int* state_slots, const int* seq_start, void* out, int out_dtype, long long ldo, int n_seqs, int max_new, int C,
+                int act, void* stream);
+int hb_selective_scan(const void* u, int u_dtype, long long ldu, const float* dbc, long long ldd, const float* z, long long ldz,
+                      const float* w_dt, const float* b_dt, const float* a_log, const float* dvec, float* state, long long state_stride,
+                      const int* state_slots, const int* seq_start, void* out, int out_dtype, long long ldo, int n_seqs, int inner,
+                      int n_state, int dt_rank, void* stream);
+// Mixture of experts (moe.cu)
+int hb_moe_route(const void* h, int h_dtype, long long ldh, const float* w_router, int* experts, float* weights, int n_tokens, int width,
+                 int n_experts, int top, void* stream);
+int hb_moe_plan(const int* experts, int n_entries, int n_experts, int* offsets, int* order, int* tiles, void* stream);
+int hb_moe_max_tiles(int n_entries, int n_experts);
+int hb_moe_glu(const void* h, int h_dtype, long long ldh, const void* w_gate, const void* w_up, int w_dtype, const int* offsets,
+               const int* order, const int* tiles, int max_tiles, int top, void* act, int act_dtype, long long lda, int ff, int width,
+               float limit, float alpha, void* stream);
+int hb_moe_down(const void* act, int act_dtype, long long lda, const void* w_down, int w_dtype, const int* offsets, const int* order,
+                const int* tiles, int max_tiles, int top, float* down, long long ldd, int width, int ff, void* stream);
+int hb_moe_combine(const float* down, long long ldd, const float* weights, int top, float* out, long long ldo, int n_tokens, int width,
+                   int accumulate, void* stream);
+int hb_glu_clamp(const float* in, long long ldi, void* out, int out_dtype, long long ldo, int n_rows, int F, float limit, float alpha,
+                 void* stream);
+
 #ifdef __cplusplus
 }
 #endif

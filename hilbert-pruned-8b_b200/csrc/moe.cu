@@ -1,0 +1,308 @@
+// Mixture of experts: router, plan, the experts' products over the tokens routed to them, and
+// the weighted sum.
+//
+// moe_route:  z = Wr h in 32-bit; the `top` largest logits of a token (lowest index on ties) are
+//             its experts, their weights softmax over those logits alone.
+// moe_plan:   entries (token, k) ordered by expert: offsets[e] .. offsets[e + 1] index `order`, whose
+//             values are entry numbers token * top + k; plus the list of (expert, first row) tiles
+//             of MOE_BM rows that the two products walk.  One block; the grid of the products is
+//             sized for the worst case and blocks beyond the last tile leave at once, so nothing
+//             is read back by the host.
+// moe_glu:    act[slot] = f(Wg_e h_token, Wu_e h_token) for the rows of an expert's tiles, with
+//             f(g, u) = g' sigmoid(alpha g') (u' + 1), g' = min(g, limit), u' = clamp(u, -limit, limit).
+// moe_down:   down[entry] = Wd_e act[slot] (32-bit), written at the ENTRY's row, so that
+// moe_combine: out[token] (+)= sum_k weight[token][k] down[token * top + k], in k order.
+// The order of the entries inside an expert's range depends on the atomics of the plan; an entry's
+// numbers do not, since every output element is one sequential sum over K.
+//
+// The products are tiled FP32-pipe kernels (MOE_BM rows x MOE_BN columns x MOE_BK): they serve
+// both precisions, with 32-bit accumulation.  glu_clamp is the same activation for a dense
+// [gate | up] matrix (a shared expert, whose products are ordinary matrix products).
+#include "api.h"
+#include "common.cuh"
+
+#define MOE_BM 32
+#define MOE_BN 32
+#define MOE_BK 32
+#define MOE_THREADS 256
+
+// ------------------------------------------------------------------------------------------------ route
+template <typename TH>
+__global__ void __launch_bounds__(256)
+moe_route_kernel(const TH* __restrict__ h, long long ldh, const float* __restrict__ wr, int* __restrict__ experts,
+                 float* __restrict__ weights, int W, int E, int top) {
+    pdl_trigger();
+    pdl_wait();
+    h = pdl_fresh(h);
+    extern __shared__ float mr_smem[];
+    float* hs = mr_smem;             // [W]
+    float* zs = hs + W;              // [E]
+    const int t = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    for (int i = tid; i < W; i += 256) hs[i] = to_f32(h[(size_t)t * ldh + i]);
+    __syncthreads();
+    for (int e = warp; e < E; e += 8) {
+        const float* w = wr + (size_t)e * W;
+        float s = 0.0f;
+        for (int i = lane; i < W; i += 32) s = fmaf(w[i], hs[i], s);
+        s = warp_sum(s);
+        if (lane == 0) zs[e] = s;
+    }
+    __syncthreads();
+    if (warp == 0) {
+        // `top` rounds of: the largest logit not yet taken, lowest index on ties
+        float zmax = 0.0f, denom = 0.0f;
+        for (int k = 0; k < top; k++) {
+            float best = -INFINITY;
+            int best_e = 0x7fffffff;
+            for (int e = lane; e < E; e += 32) {
+                const float v = zs[e];
+                if (v > best || (v == best && e < best_e)) { best = v; best_e = e; }
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+                const int oe = __shfl_xor_sync(0xffffffffu, best_e, o);
+                if (ob > best || (ob == best && oe < best_e)) { best = ob; best_e = oe; }
+            }
+            if (best_e >= E) best_e = 0;                  // a row of logits that are not numbers: any expert, the result is not finite anyway
+            if (k == 0) zmax = best;
+            const float p = expf(best - zmax);
+            denom += p;
+            if (lane == 0) {
+                experts[(size_t)t * top + k] = best_e;
+                weights[(size_t)t * top + k] = p;
+                zs[best_e] = -INFINITY;
+            }
+            __syncwarp();
+        }
+        if (lane == 0)
+            for (int k = 0; k < top; k++) weights[(size_t)t * top + k] /= denom;
+    }
+}
+
+extern "C" int hb_moe_route(const void* h, int h_dtype, long long ldh, const float* w_router, int* experts, float* weights,
+                            int n_tokens, int width, int n_experts, int top, void* stream) {
+    if (n_tokens == 0) return 0;
+    HB_REQUIRE(n_tokens > 0 && width > 0 && n_experts > 0 && top >= 1 && top <= n_experts, "moe_route: bad sizes");
+    const size_t smem = sizeof(float) * ((size_t)width + n_experts);
+    HB_REQUIRE(smem <= 48 * 1024, "moe_route: width + experts = %d is too wide", width + n_experts);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (h_dtype == HB_BF16)
+        hb_launch(moe_route_kernel<bf16>, dim3(n_tokens), dim3(256), smem, s, (const bf16*)h, ldh, w_router, experts, weights, width, n_experts, top);
+    else if (h_dtype == HB_F32)
+        hb_launch(moe_route_kernel<float>, dim3(n_tokens), dim3(256), smem, s, (const float*)h, ldh, w_router, experts, weights, width, n_experts, top);
+    else return hb_fail("moe_route: unsupported dtype %d", h_dtype);
+    return hb_check_launch("moe_route");
+}
+
+// ------------------------------------------------------------------------------------------------ plan
+// offsets [E + 1], order [entries], tiles [1 + 2 * max_tiles]: tiles[0] = number of tiles, then (expert, first row) pairs
+__global__ void __launch_bounds__(1024)
+moe_plan_kernel(const int* __restrict__ experts, int n_entries, int E, int* __restrict__ offsets, int* __restrict__ order,
+                int* __restrict__ tiles) {
+    pdl_trigger();
+    pdl_wait();
+    experts = pdl_fresh(experts);
+    extern __shared__ int mp_smem[];
+    int* count = mp_smem;            // [E]
+    int* cursor = count + E;         // [E]
+    const int tid = threadIdx.x;
+    for (int e = tid; e < E; e += 1024) count[e] = 0;
+    __syncthreads();
+    for (int i = tid; i < n_entries; i += 1024) atomicAdd(&count[experts[i]], 1);
+    __syncthreads();
+    if (tid == 0) {
+        int at = 0, nt = 0;
+        for (int e = 0; e < E; e++) {
+            offsets[e] = at;
+            cursor[e] = at;
+            for (int r = 0; r < count[e]; r += MOE_BM) {
+                tiles[1 + 2 * nt] = e;
+                tiles[2 + 2 * nt] = at + r;
+                nt++;
+            }
+            at += count[e];
+        }
+        offsets[E] = at;
+        tiles[0] = nt;
+    }
+    __syncthreads();
+    for (int i = tid; i < n_entries; i += 1024) order[atomicAdd(&cursor[experts[i]], 1)] = i;
+}
+
+extern "C" int hb_moe_plan(const int* experts, int n_entries, int n_experts, int* offsets, int* order, int* tiles, void* stream) {
+    if (n_entries == 0) return 0;
+    HB_REQUIRE(n_entries > 0 && n_experts > 0 && n_experts <= 4096, "moe_plan: bad sizes");
+    hb_launch(moe_plan_kernel, dim3(1), dim3(1024), sizeof(int) * 2 * n_experts, (cudaStream_t)stream, experts, n_entries, n_experts, offsets,
+              order, tiles);
+    return hb_check_launch("moe_plan");
+}
+
+extern "C" int hb_moe_max_tiles(int n_entries, int n_experts) { return (n_entries + MOE_BM - 1) / MOE_BM + n_experts; }
+
+// ------------------------------------------------------------------------------------------------ the experts' products
+__device__ __forceinline__ float moe_glu(float g, float u, float limit, float alpha) {
+    g = fminf(g, limit);
+    u = fminf(fmaxf(u, -limit), limit);
+    return g * (1.0f / (1.0f + expf(-alpha * g))) * (u + 1.0f);
+}
+
+// GLU: a rows are h[token of the entry], two weight matrices [E][N][K], result act[slot][N] in TO.
+// else: a rows are act[slot], one weight matrix, result down[entry][N] in 32-bit.
+template <typename TA, typename TW, typename TO, bool GLU>
+__global__ void __launch_bounds__(MOE_THREADS)
+moe_product_kernel(const TA* __restrict__ a, long long lda, const TW* __restrict__ w0, const TW* __restrict__ w1,
+                   const int* __restrict__ offsets, const int* __restrict__ order, const int* __restrict__ tiles, int top,
+                   TO* __restrict__ out, long long ldo, int N, int K, float limit, float alpha) {
+    pdl_trigger();
+    __shared__ float As[MOE_BK][MOE_BM + 1];
+    __shared__ float B0[MOE_BK][MOE_BN + 1];
+    __shared__ float B1[GLU ? MOE_BK : 1][MOE_BN + 1];
+    __shared__ int row_src[MOE_BM], row_dst[MOE_BM];
+    pdl_wait();
+    a = pdl_fresh(a);
+    tiles = pdl_fresh(tiles);
+    order = pdl_fresh(order);
+    offsets = pdl_fresh(offsets);
+    if ((int)blockIdx.x >= tiles[0]) return;
+    const int e = tiles[1 + 2 * blockIdx.x], r0 = tiles[2 + 2 * blockIdx.x];
+    const int rows = min(MOE_BM, offsets[e + 1] - r0);
+    const int n0 = blockIdx.y * MOE_BN;
+    const int tid = threadIdx.x;
+    if (tid < MOE_BM) {
+        const int entry = tid < rows ? order[r0 + tid] : -1;
+        row_src[tid] = entry < 0 ? -1 : (GLU ? entry / top : r0 + tid);
+        row_dst[tid] = entry < 0 ? -1 : (GLU ? r0 + tid : entry);
+    }
+    __syncthreads();
+    const TW* we0 = w0 + (size_t)e * N * K;
+    const TW* we1 = GLU ? w1 + (size_t)e * N * K : nullptr;
+    // thread -> rows ty * 2 + {0, 1}, columns tx * 2 + {0, 1}
+    const int tx = tid & 15, ty = tid >> 4;
+    float acc0[2][2] = {{0.0f, 0.0f}, {0.0f, 0.0f}}, acc1[2][2] = {{0.0f, 0.0f}, {0.0f, 0.0f}};
+    for (int k0 = 0; k0 < K; k0 += MOE_BK) {
+        for (int i = tid; i < MOE_BM * MOE_BK; i += MOE_THREADS) {
+            const int r = i / MOE_BK, k = i - r * MOE_BK;
+            const int src = row_src[r];
+            As[k][r] = (src >= 0 && k0 + k < K) ? to_f32(a[(size_t)src * lda + k0 + k]) : 0.0f;
+        }
+        for (int i = tid; i < MOE_BN * MOE_BK; i += MOE_THREADS) {
+            const int n = i / MOE_BK, k = i - n * MOE_BK;
+            const bool in = n0 + n < N && k0 + k < K;
+            B0[k][n] = in ? to_f32(we0[(size_t)(n0 + n) * K + k0 + k]) : 0.0f;
+            if (GLU) B1[k][n] = in ? to_f32(we1[(size_t)(n0 + n) * K + k0 + k]) : 0.0f;
+        }
+        __syncthreads();
+#pragma unroll 8
+        for (int k = 0; k < MOE_BK; k++) {
+            const float a0 = As[k][ty * 2], a1 = As[k][ty * 2 + 1];
+            const float b0 = B0[k][tx * 2], b1 = B0[k][tx * 2 + 1];
+            acc0[0][0] = fmaf(a0, b0, acc0[0][0]);
+            acc0[0][1] = fmaf(a0, b1, acc0[0][1]);
+            acc0[1][0] = fmaf(a1, b0, acc0[1][0]);
+            acc0[1][1] = fmaf(a1, b1, acc0[1][1]);
+            if (GLU) {
+                const float c0 = B1[k][tx * 2], c1 = B1[k][tx * 2 + 1];
+                acc1[0][0] = fmaf(a0, c0, acc1[0][0]);
+                acc1[0][1] = fmaf(a0, c1, acc1[0][1]);
+                acc1[1][0] = fmaf(a1, c0, acc1[1][0]);
+                acc1[1][1] = fmaf(a1, c1, acc1[1][1]);
+            }
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < 2; i++) {
+        const int dst = row_dst[ty * 2 + i];
+        if (dst < 0) continue;
+#pragma unroll
+        for (int j = 0; j < 2; j++) {
+            const int n = n0 + tx * 2 + j;
+            if (n >= N) continue;
+            const float v = GLU ? moe_glu(acc0[i][j], acc1[i][j], limit, alpha) : acc0[i][j];
+            out[(size_t)dst * ldo + n] = from_f32<TO>(v);
+        }
+    }
+}
+
+extern "C" int hb_moe_glu(const void* h, int h_dtype, long long ldh, const void* w_gate, const void* w_up, int w_dtype, const int* offsets,
+                          const int* order, const int* tiles, int max_tiles, int top, void* act, int act_dtype, long long lda, int ff,
+                          int width, float limit, float alpha, void* stream) {
+    HB_REQUIRE(max_tiles > 0 && ff > 0 && width > 0 && top >= 1, "moe_glu: bad sizes");
+    HB_REQUIRE((ff + MOE_BN - 1) / MOE_BN <= 65535, "moe_glu: too many columns");
+    dim3 grid(max_tiles, (ff + MOE_BN - 1) / MOE_BN);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (h_dtype == HB_BF16 && w_dtype == HB_BF16 && act_dtype == HB_BF16)
+        hb_launch(moe_product_kernel<bf16, bf16, bf16, true>, dim3(grid), dim3(MOE_THREADS), 0, s, (const bf16*)h, ldh, (const bf16*)w_gate,
+                  (const bf16*)w_up, offsets, order, tiles, top, (bf16*)act, lda, ff, width, limit, alpha);
+    else if (h_dtype == HB_F32 && w_dtype == HB_F32 && act_dtype == HB_F32)
+        hb_launch(moe_product_kernel<float, float, float, true>, dim3(grid), dim3(MOE_THREADS), 0, s, (const float*)h, ldh, (const float*)w_gate,
+                  (const float*)w_up, offsets, order, tiles, top, (float*)act, lda, ff, width, limit, alpha);
+    else return hb_fail("moe_glu: unsupported dtypes h %d w %d act %d", h_dtype, w_dtype, act_dtype);
+    return hb_check_launch("moe_glu");
+}
+
+extern "C" int hb_moe_down(const void* act, int act_dtype, long long lda, const void* w_down, int w_dtype, const int* offsets, const int* order,
+                           const int* tiles, int max_tiles, int top, float* down, long long ldd, int width, int ff, void* stream) {
+    HB_REQUIRE(max_tiles > 0 && ff > 0 && width > 0, "moe_down: bad sizes");
+    HB_REQUIRE((width + MOE_BN - 1) / MOE_BN <= 65535, "moe_down: too many columns");
+    dim3 grid(max_tiles, (width + MOE_BN - 1) / MOE_BN);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (act_dtype == HB_BF16 && w_dtype == HB_BF16)
+        hb_launch(moe_product_kernel<bf16, bf16, float, false>, dim3(grid), dim3(MOE_THREADS), 0, s, (const bf16*)act, lda, (const bf16*)w_down,
+                  (const bf16*)nullptr, offsets, order, tiles, top, down, ldd, width, ff, 0.0f, 0.0f);
+    else if (act_dtype == HB_F32 && w_dtype == HB_F32)
+        hb_launch(moe_product_kernel<float, float, float, false>, dim3(grid), dim3(MOE_THREADS), 0, s, (const float*)act, lda, (const float*)w_down,
+                  (const float*)nullptr, offsets, order, tiles, top, down, ldd, width, ff, 0.0f, 0.0f);
+    else return hb_fail("moe_down: unsupported dtypes act %d w %d", act_dtype, w_dtype);
+    return hb_check_launch("moe_down");
+}
+
+// ------------------------------------------------------------------------------------------------ combine
+__global__ void __launch_bounds__(256)
+moe_combine_kernel(const float* __restrict__ down, long long ldd, const float* __restrict__ weights, int top, float* __restrict__ out,
+                   long long ldo, int width, int accumulate) {
+    pdl_trigger();
+    pdl_wait();
+    down = pdl_fresh(down);
+    weights = pdl_fresh(weights);
+    const int t = blockIdx.x;
+    for (int c = threadIdx.x; c < width; c += 256) {
+        float v = accumulate ? out[(size_t)t * ldo + c] : 0.0f;
+        for (int k = 0; k < top; k++) v = fmaf(weights[(size_t)t * top + k], down[((size_t)t * top + k) * ldd + c], v);
+        out[(size_t)t * ldo + c] = v;
+    }
+}
+
+extern "C" int hb_moe_combine(const float* down, long long ldd, const float* weights, int top, float* out, long long ldo, int n_tokens,
+                              int width, int accumulate, void* stream) {
+    if (n_tokens == 0) return 0;
+    HB_REQUIRE(n_tokens > 0 && width > 0 && top >= 1, "moe_combine: bad sizes");
+    hb_launch(moe_combine_kernel, dim3(n_tokens), dim3(256), 0, (cudaStream_t)stream, down, ldd, weights, top, out, ldo, width, accumulate);
+    return hb_check_launch("moe_combine");
+}
+
+// ------------------------------------------------------------------------------------------------ glu_clamp
+// in [rows][2 F] = [gate | up] in 32-bit, out [rows][F]
+template <typename TO>
+__global__ void __launch_bounds__(256)
+glu_clamp_kernel(const float* __restrict__ in, long long ldi, TO* __restrict__ out, long long ldo, int F, float limit, float alpha) {
+    pdl_trigger();
+    pdl_wait();
+    in = pdl_fresh(in);
+    const float* r = in + (size_t)blockIdx.y * ldi;
+    for (int i = blockIdx.x * 256 + threadIdx.x; i < F; i += gridDim.x * 256)
+        out[(size_t)blockIdx.y * ldo + i] = from_f32<TO>(moe_glu(r[i], r[F + i], limit, alpha));
+}
+
+extern "C" int hb_glu_clamp(const float* in, long long ldi, void* out, int out_dtype, long long ldo, int n_rows, int F, float limit,
+                            float alpha, void* stream) {
+    if (n_rows == 0) return 0;
+    HB_REQUIRE(n_rows > 0 && n_rows <= 65535 && F > 0 && ldi >= 2 * F && ldo >= F, "glu_clamp: bad sizes");
+    dim3 grid(min((F + 255) / 256, 64), n_rows);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (out_dtype == HB_BF16) hb_launch(glu_clamp_kernel<bf16>, dim3(grid), dim3(256), 0, s, in, ldi, (bf16*)out, ldo, F, limit, alpha);
+    else if (out_dtype == HB_F32) hb_launch(glu_clamp_kernel<float>, dim3(grid), dim3(256), 0, s, in, ldi, (float*)out, ldo, F, limit, alpha);
+    else return hb_fail("glu_clamp: unsupported output dtype %d", out_dtype);
+    return hb_check_launch("glu_clamp");
+}

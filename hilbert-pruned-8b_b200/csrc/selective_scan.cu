@@ -1,0 +1,225 @@
+// Selective state-space scan (Mamba) and the short causal convolution in front of it.
+//
+// conv_act: u[t][c] = act(b[c] + sum_j w[c][j] x[t - taps + 1 + j][c]) per channel, zeros before a
+// sequence's first token; the last taps - 1 inputs of every sequence are its state
+// ([slot][taps - 1][C] floats), read by the step's first tokens and brought up to date.  x is a
+// column range of a wider 32-bit matrix (row stride ldx).
+//
+// selective_scan: per token t, channel c, state index n (all 32-bit):
+//   dt_c = softplus(sum_r Wdt[c][r] low[t][r] + bdt[c]),  A[c][n] = -exp(A_log[c][n])
+//   S[c][n] <- exp(dt_c A[c][n]) S[c][n] + dt_c u[t][c] B[t][n]
+//   y[t][c] = sum_n S[c][n] C[t][n] + D[c] u[t][c];   out[t][c] = y silu(z[t][c])
+// with [low | B | C] the rows of one 32-bit matrix (the result of the projection of u).  A group
+// of SS_LANES threads owns a channel (state index n = lane, lane + SS_LANES, ...); a block owns
+// SS_CH channels of one sequence and walks its tokens in order, SS_TOK tokens of inputs staged
+// in shared memory at a time.  The state is read once and written once per step.
+#include "api.h"
+#include "common.cuh"
+
+#define CA_CH 32
+#define CA_TL 8
+#define CA_RUN 256
+#define CA_MAX_TAPS 16
+
+template <typename TO>
+__global__ void __launch_bounds__(CA_CH * CA_TL)
+conv_act_kernel(const float* __restrict__ x, long long ldx, const float* __restrict__ cw, const float* __restrict__ cb, int taps,
+                float* __restrict__ state, long long state_stride, const int* __restrict__ state_slots,
+                const int* __restrict__ seq_start, TO* __restrict__ out, long long ldo, int C, int act) {
+    pdl_trigger();
+    const int c = blockIdx.x * CA_CH + (threadIdx.x & (CA_CH - 1));
+    const int tl = threadIdx.x / CA_CH;
+    const int b = blockIdx.y;
+    const bool live = c < C;
+    const int hist = taps - 1;
+    float w[CA_MAX_TAPS], st[CA_MAX_TAPS];
+#pragma unroll
+    for (int j = 0; j < CA_MAX_TAPS; j++) w[j] = (live && j < taps) ? cw[(size_t)c * taps + j] : 0.0f;
+    const float bias = (live && cb != nullptr) ? cb[c] : 0.0f;
+    const int start = seq_start[b], n = seq_start[b + 1] - start;
+    const int t_begin = blockIdx.z * CA_RUN, t_end = min(n, t_begin + CA_RUN);
+    if (t_begin >= n) return;
+    const bool first = blockIdx.z == 0;        // only a sequence's first run looks back beyond the step and owns the state
+    float* srow = state + (size_t)state_slots[b] * state_stride;
+    pdl_wait();
+    x = pdl_fresh(x);
+    srow = pdl_fresh(srow);
+#pragma unroll
+    for (int j = 0; j < CA_MAX_TAPS; j++) st[j] = (first && live && j < hist) ? srow[(size_t)j * C + c] : 0.0f;
+    __syncthreads();                           // every thread has the old state before anyone writes the new one
+    auto input = [&](int src) -> float {       // the sequence's input `src` of this step, or of an earlier step (src < 0)
+        if (src < 0) {
+            float v = 0.0f;
+#pragma unroll
+            for (int j = 0; j < CA_MAX_TAPS; j++) v = (j == hist + src) ? st[j] : v;
+            return v;
+        }
+        return x[(size_t)(start + src) * ldx + c];
+    };
+    if (!live) return;
+    for (int t = t_begin + tl; t < t_end; t += CA_TL) {
+        float acc = bias;
+#pragma unroll
+        for (int j = 0; j < CA_MAX_TAPS; j++)
+            if (j < taps) acc = fmaf(w[j], input(t - hist + j), acc);
+        if (act == 1) acc = acc / (1.0f + expf(-acc));
+        out[(size_t)(start + t) * ldo + c] = from_f32<TO>(acc);
+    }
+    if (first && tl == 0)
+        for (int j = 0; j < hist; j++) srow[(size_t)j * C + c] = input(n - hist + j);
+}
+
+extern "C" int hb_conv_act(const float* x, long long ldx, const float* conv_w, const float* conv_b, int taps, float* state,
+                           long long state_stride, const int* state_slots, const int* seq_start, void* out, int out_dtype,
+                           long long ldo, int n_seqs, int max_new, int C, int act, void* stream) {
+    if (n_seqs == 0) return 0;
+    HB_REQUIRE(n_seqs > 0 && n_seqs <= 65535 && C > 0 && ldx >= C && ldo >= C && max_new >= 1, "conv_act: bad sizes");
+    HB_REQUIRE(taps >= 1 && taps <= CA_MAX_TAPS, "conv_act: %d taps (1..%d are built)", taps, CA_MAX_TAPS);
+    static_assert(CA_RUN >= CA_MAX_TAPS - 1, "a sequence's first run holds every token that looks back beyond the step");
+    HB_REQUIRE((max_new + CA_RUN - 1) / CA_RUN <= 65535, "conv_act: too many tokens in one sequence's step");
+    HB_REQUIRE(act == 0 || act == 1, "conv_act: activation %d (0 none, 1 silu)", act);
+    dim3 grid((C + CA_CH - 1) / CA_CH, n_seqs, (max_new + CA_RUN - 1) / CA_RUN), block(CA_CH * CA_TL);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (out_dtype == HB_BF16)
+        hb_launch(conv_act_kernel<bf16>, dim3(grid), dim3(block), 0, s, x, ldx, conv_w, conv_b, taps, state, state_stride, state_slots, seq_start,
+                  (bf16*)out, ldo, C, act);
+    else if (out_dtype == HB_F32)
+        hb_launch(conv_act_kernel<float>, dim3(grid), dim3(block), 0, s, x, ldx, conv_w, conv_b, taps, state, state_stride, state_slots, seq_start,
+                  (float*)out, ldo, C, act);
+    else return hb_fail("conv_act: unsupported output dtype %d", out_dtype);
+    return hb_check_launch("conv_act");
+}
+
+// ------------------------------------------------------------------------------------------------ selective_scan
+#define SS_THREADS 256
+#define SS_TOK 16           // tokens of inputs staged at a time
+#define SS_MAX_PER 8        // state values a thread holds: state sizes up to SS_MAX_PER * lanes
+
+__device__ __forceinline__ float ss_softplus(float z) { return z > 20.0f ? z : log1pf(expf(z)); }
+
+template <typename TU, typename TO, int LANES>
+__global__ void __launch_bounds__(SS_THREADS)
+selective_scan_kernel(const TU* __restrict__ u, long long ldu, const float* __restrict__ dbc, long long ldd,
+                      const float* __restrict__ z, long long ldz, const float* __restrict__ w_dt, const float* __restrict__ b_dt,
+                      const float* __restrict__ a_log, const float* __restrict__ dvec, float* __restrict__ state,
+                      long long state_stride, const int* __restrict__ state_slots, const int* __restrict__ seq_start,
+                      TO* __restrict__ out, long long ldo, int I, int N, int R) {
+    pdl_trigger();
+    constexpr int CH = SS_THREADS / LANES;             // channels per block
+    extern __shared__ float ss_smem[];
+    float* rows = ss_smem;                             // [SS_TOK][R + 2 N]: low | B | C of the staged tokens
+    float* us = rows + SS_TOK * (R + 2 * N);           // [SS_TOK][CH]
+    float* zs = us + SS_TOK * CH;                      // [SS_TOK][CH]
+    const int tid = threadIdx.x, lane = tid % LANES, ch = tid / LANES;
+    const int c = blockIdx.x * CH + ch, b = blockIdx.y;
+    const bool live = c < I;
+    const int start = seq_start[b], n_all = seq_start[b + 1] - start;
+    const int wrow = R + 2 * N;
+    float A[SS_MAX_PER], S[SS_MAX_PER];
+#pragma unroll
+    for (int k = 0; k < SS_MAX_PER; k++) {
+        const int n = lane + k * LANES;
+        A[k] = (live && n < N) ? -expf(a_log[(size_t)c * N + n]) : 0.0f;
+    }
+    const float bdt = live ? b_dt[c] : 0.0f, D = live ? dvec[c] : 0.0f;
+    const float* wd = w_dt + (size_t)(live ? c : 0) * R;
+    pdl_wait();
+    u = pdl_fresh(u);
+    dbc = pdl_fresh(dbc);
+    z = pdl_fresh(z);
+    state = pdl_fresh(state);
+    float* srow = state + (size_t)state_slots[b] * state_stride + (size_t)(live ? c : 0) * N;
+#pragma unroll
+    for (int k = 0; k < SS_MAX_PER; k++) {
+        const int n = lane + k * LANES;
+        S[k] = (live && n < N) ? srow[n] : 0.0f;
+    }
+    for (int base = 0; base < n_all; base += SS_TOK) {
+        const int nt = min(SS_TOK, n_all - base);
+        __syncthreads();
+        for (int i = tid; i < nt * wrow; i += SS_THREADS) {
+            const int j = i / wrow, r = i - j * wrow;
+            rows[j * wrow + r] = dbc[(size_t)(start + base + j) * ldd + r];
+        }
+        for (int i = tid; i < nt * CH; i += SS_THREADS) {
+            const int j = i / CH, k = i - j * CH, cc = blockIdx.x * CH + k;
+            us[i] = cc < I ? to_f32(u[(size_t)(start + base + j) * ldu + cc]) : 0.0f;
+            zs[i] = cc < I ? z[(size_t)(start + base + j) * ldz + cc] : 0.0f;
+        }
+        __syncthreads();
+        for (int j = 0; j < nt; j++) {
+            const float* row = rows + j * wrow;
+            float part = 0.0f;
+            for (int r = lane; r < R; r += LANES) part = fmaf(wd[r], row[r], part);
+#pragma unroll
+            for (int o = LANES / 2; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o, LANES);
+            const float dt = ss_softplus(part + bdt);
+            const float uv = us[j * CH + ch];
+            const float dtu = dt * uv;
+            float y = 0.0f;
+#pragma unroll
+            for (int k = 0; k < SS_MAX_PER; k++) {
+                const int n = lane + k * LANES;
+                if (n < N) {
+                    S[k] = fmaf(expf(dt * A[k]), S[k], dtu * row[R + n]);
+                    y = fmaf(S[k], row[R + N + n], y);
+                }
+            }
+#pragma unroll
+            for (int o = LANES / 2; o > 0; o >>= 1) y += __shfl_xor_sync(0xffffffffu, y, o, LANES);
+            if (lane == 0 && live) {
+                const float zv = zs[j * CH + ch];
+                out[(size_t)(start + base + j) * ldo + c] = from_f32<TO>((y + D * uv) * (zv / (1.0f + expf(-zv))));
+            }
+        }
+    }
+    if (live) {
+#pragma unroll
+        for (int k = 0; k < SS_MAX_PER; k++) {
+            const int n = lane + k * LANES;
+            if (n < N) srow[n] = S[k];
+        }
+    }
+}
+
+static int ss_lanes(int N) { return N <= 4 ? 4 : N <= 8 ? 8 : N <= 16 ? 16 : 32; }
+
+extern "C" int hb_selective_scan(const void* u, int u_dtype, long long ldu, const float* dbc, long long ldd, const float* z, long long ldz,
+                                 const float* w_dt, const float* b_dt, const float* a_log, const float* dvec, float* state,
+                                 long long state_stride, const int* state_slots, const int* seq_start, void* out, int out_dtype,
+                                 long long ldo, int n_seqs, int inner, int n_state, int dt_rank, void* stream) {
+    if (n_seqs == 0) return 0;
+    HB_REQUIRE(n_seqs > 0 && n_seqs <= 65535 && inner > 0 && n_state > 0 && dt_rank > 0, "selective_scan: bad sizes");
+    HB_REQUIRE(n_state <= SS_MAX_PER * 32, "selective_scan: state size %d (up to %d is built)", n_state, SS_MAX_PER * 32);
+    HB_REQUIRE(ldd >= dt_rank + 2 * n_state && ldu >= inner && ldz >= inner && ldo >= inner && state_stride >= (long long)inner * n_state,
+               "selective_scan: rows are too short");
+    HB_REQUIRE(u_dtype == out_dtype && (u_dtype == HB_BF16 || u_dtype == HB_F32), "selective_scan: unsupported dtypes %d -> %d", u_dtype, out_dtype);
+    const int lanes = ss_lanes(n_state), ch = SS_THREADS / lanes;
+    const size_t smem = sizeof(float) * ((size_t)SS_TOK * (dt_rank + 2 * n_state) + 2 * SS_TOK * ch);
+    HB_REQUIRE(smem <= 200 * 1024, "selective_scan: dt_rank + 2 * state = %d is too wide for the staging buffer", dt_rank + 2 * n_state);
+    dim3 grid((inner + ch - 1) / ch, n_seqs);
+    cudaStream_t s = (cudaStream_t)stream;
+#define HB_SS(TU, TO, L)                                                                                                                  \
+    do {                                                                                                                                  \
+        static bool done[HB_MAX_DEVICES] = {};                                                                                            \
+        const int slot = hb_device_slot();                                                                                                \
+        if (!done[slot]) {                                                                                                                \
+            cudaError_t e = cudaFuncSetAttribute(selective_scan_kernel<TU, TO, L>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024); \
+            if (e != cudaSuccess) return hb_fail("selective_scan: shared memory: %s", cudaGetErrorString(e));                             \
+            done[slot] = true;                                                                                                            \
+        }                                                                                                                                 \
+        hb_launch(selective_scan_kernel<TU, TO, L>, dim3(grid), dim3(SS_THREADS), smem, s, (const TU*)u, ldu, dbc, ldd, z, ldz, w_dt, b_dt, \
+                  a_log, dvec, state, state_stride, state_slots, seq_start, (TO*)out, ldo, inner, n_state, dt_rank);                       \
+    } while (0)
+#define HB_SS_L(TU, TO)                                                                          \
+    switch (lanes) {                                                                             \
+        case 4: HB_SS(TU, TO, 4); break;                                                         \
+        case 8: HB_SS(TU, TO, 8); break;                                                         \
+        case 16: HB_SS(TU, TO, 16); break;                                                       \
+        default: HB_SS(TU, TO, 32); break;                                                       \
+    }
+    if (u_dtype == HB_BF16) { HB_SS_L(bf16, bf16) } else { HB_SS_L(float, float) }
+#undef HB_SS_L
+#undef HB_SS
+    return hb_check_launch("selective_scan");
+}

@@ -76,6 +76,29 @@ _SIGNATURES = {
     "hb_random_normal": [_c_ptr, _c_int, _c_ll, ctypes.c_ulonglong, _c_float, _c_float, _c_ptr],
     "hb_argmax": [_c_ptr, _c_ll, _c_ptr, _c_int, _c_int, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_ptr],
     "hb_sample": [_c_ptr, _c_ll, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_ptr, _c_ptr],
+    "hb_rmsnorm_add": [_c_ptr, _c_ll, _c_ptr, _c_float, _c_float, _c_ptr, _c_ll, _c_ptr, _c_float, _c_float, _c_ptr, _c_int, _c_ll, _c_int,
+                       _c_int, _c_ptr],
+    "hb_scaled_sum": [_c_ptr, _c_float, _c_ptr, _c_float, _c_ptr, _c_ll, _c_ptr],
+    "hb_qk_norm_append": [_c_ptr, _c_ll, _c_ptr, _c_ptr, _c_float, _c_ptr, _c_int, _c_ll, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_int, _c_ptr,
+                          _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr, _c_ptr],
+    "hb_pool_blocks": [_c_ptr, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int,
+                       _c_int, _c_int, _c_int, _c_int, _c_ptr, _c_ptr],
+    "hb_attention_pool": [_c_ptr, _c_int, _c_ll, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_int,
+                          _c_int, _c_ptr, _c_ptr, _c_ll, _c_ptr, _c_int, _c_ll, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float,
+                          _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr, _c_ptr],
+    "hb_decay_memory": [_c_ptr, _c_ll, _c_ptr, _c_ptr, _c_ll, _c_ptr, _c_ptr, _c_ptr, _c_ll, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr],
+    "hb_gated_norm": [_c_ptr, _c_ll, _c_ptr, _c_ll, _c_ptr, _c_float, _c_float, _c_ptr, _c_int, _c_ll, _c_int, _c_int, _c_ptr],
+    "hb_conv_act": [_c_ptr, _c_ll, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_ll, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_ll, _c_int, _c_int, _c_int,
+                    _c_int, _c_ptr],
+    "hb_selective_scan": [_c_ptr, _c_int, _c_ll, _c_ptr, _c_ll, _c_ptr, _c_ll, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ll, _c_ptr, _c_ptr,
+                          _c_ptr, _c_int, _c_ll, _c_int, _c_int, _c_int, _c_int, _c_ptr],
+    "hb_moe_route": [_c_ptr, _c_int, _c_ll, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_ptr],
+    "hb_moe_plan": [_c_ptr, _c_int, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_ptr],
+    "hb_moe_glu": [_c_ptr, _c_int, _c_ll, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_ptr, _c_int, _c_ll, _c_int,
+                   _c_int, _c_float, _c_float, _c_ptr],
+    "hb_moe_down": [_c_ptr, _c_int, _c_ll, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_ptr, _c_ll, _c_int, _c_int, _c_ptr],
+    "hb_moe_combine": [_c_ptr, _c_ll, _c_ptr, _c_int, _c_ptr, _c_ll, _c_int, _c_int, _c_int, _c_ptr],
+    "hb_glu_clamp": [_c_ptr, _c_ll, _c_ptr, _c_int, _c_ll, _c_int, _c_int, _c_float, _c_float, _c_ptr],
 }
 
 _DTYPE_CODE = {torch.float32: 0, torch.bfloat16: 1}
@@ -110,6 +133,8 @@ def load_library():
         lib.hb_attention_sink_prefill_supported.argtypes, lib.hb_attention_sink_prefill_supported.restype = [_c_int] * 4, _c_int
         lib.hb_attention_heads_variant.argtypes, lib.hb_attention_heads_variant.restype = [_c_int] * 6, _c_int
         lib.hb_attention_heads_writes_output.argtypes, lib.hb_attention_heads_writes_output.restype = [_c_int] * 6, _c_int
+        lib.hb_attention_pool_supported.argtypes, lib.hb_attention_pool_supported.restype = [_c_int] * 2, _c_int
+        lib.hb_moe_max_tiles.argtypes, lib.hb_moe_max_tiles.restype = [_c_int] * 2, _c_int
         lib.hb_attention_decode_ctas_per_sm.argtypes, lib.hb_attention_decode_ctas_per_sm.restype = [_c_int], _c_int
         lib.hb_attention_decode_scratch_floats.argtypes = [_c_int, _c_int, _c_int, _c_int]
         lib.hb_attention_decode_scratch_floats.restype = _c_ll
@@ -944,6 +969,244 @@ class Ops:
                    step.tok_seq.data_ptr(), step.positions.data_ptr(), out.data_ptr(), _code(out),
                    _rows(out, "attention output"), T, heads, kv_heads, head_dim, float(scale), win, cache.k.shape[0],
                    self.status.data_ptr(), self._stream())
+        self.launches += 1
+
+    # ------------------------------------------------------------------ norms on a sublayer's output
+    def rmsnorm_add(self, y, weight, eps: float, offset: float, x, then=None, then_out=None) -> None:
+        """``x += y / sqrt(mean(y^2) + eps) * (offset + weight)`` row by row in 32-bit; with ``then = (weight2, eps2,
+        offset2)`` and ``then_out`` also ``then_out = x / sqrt(mean(x^2) + eps2) * (offset2 + weight2)`` of the new rows."""
+        self._dev(y, weight, x, then_out)
+        T, n = x.shape
+        if y.dtype != torch.float32 or x.dtype != torch.float32 or tuple(y.shape) != (T, n) or (then is None) != (then_out is None):
+            raise KernelError("rmsnorm_add: float32 [tokens, width] input and residual expected")
+        w2 = e2 = o2 = None
+        if then is not None:
+            w2, e2, o2 = then
+            if tuple(then_out.shape) != (T, n):
+                raise KernelError("rmsnorm_add: the second norm's output does not match")
+        self._call("hb_rmsnorm_add", y.data_ptr(), _rows(y, "rmsnorm_add input"), self._f32_vec(weight, n, "norm weight"), float(eps),
+                   float(offset), x.data_ptr(), _rows(x, "residual"), self._f32_vec(w2, n, "norm weight") if then is not None else None,
+                   float(e2 or 0.0), float(o2 or 0.0), then_out.data_ptr() if then is not None else None,
+                   _code(then_out) if then is not None else 0, _rows(then_out, "norm output") if then is not None else 0, T, n,
+                   self._stream())
+        self.launches += 1
+
+    def scaled_sum(self, a, sa: float, b, sb: float, out) -> None:
+        """``out = sa * a + sb * b`` over contiguous float32 tensors of one shape (``out`` may be ``a`` or ``b``)."""
+        self._dev(a, b, out)
+        if any(t.dtype != torch.float32 or not t.is_contiguous() or t.shape != out.shape for t in (a, b, out)):
+            raise KernelError("scaled_sum: contiguous float32 tensors of one shape expected")
+        self._call("hb_scaled_sum", a.data_ptr(), float(sa), b.data_ptr(), float(sb), out.data_ptr(), out.numel(), self._stream())
+        self.launches += 1
+
+    # ------------------------------------------------------------------ window + pooled blocks, sigmoid weights
+    def qk_norm_append(self, proj, q_weight, k_weight, eps: float, heads: int, kv_heads: int, head_dim: int, v_dim: int, q_out, cache,
+                       step, append: bool) -> None:
+        """From a step's float32 projections ``[q | k | v | ...]``: with weights, q and k are divided by the root mean square of
+        the token's WHOLE query (key) projection and multiplied by them; queries to ``q_out``, keys and values into the cache."""
+        self._dev(proj, q_weight, k_weight, q_out, cache.k, cache.v)
+        T = proj.shape[0]
+        if proj.dtype != torch.float32 or tuple(q_out.shape) != (T, heads * head_dim):
+            raise KernelError("qk_norm_append: float32 projections and [tokens, heads * head_dim] queries expected")
+        if tuple(cache.k.shape[1:]) != (kv_heads, 64, head_dim) or tuple(cache.v.shape[1:]) != (kv_heads, 64, v_dim) \
+                or not cache.k.is_contiguous() or not cache.v.is_contiguous() or cache.k.dtype != cache.v.dtype:
+            raise KernelError("qk_norm_append: cache layer does not match the heads")
+        pt = step.page_tables[cache.group]
+        self._call("hb_qk_norm_append", proj.data_ptr(), _rows(proj, "projections"),
+                   self._f32_vec(q_weight, heads * head_dim, "query norm weight") if q_weight is not None else None,
+                   self._f32_vec(k_weight, kv_heads * head_dim, "key norm weight") if k_weight is not None else None, float(eps),
+                   q_out.data_ptr(), _code(q_out), _rows(q_out, "queries"), cache.k.data_ptr(), cache.v.data_ptr(), _code(cache.k),
+                   pt.data_ptr(), pt.shape[1], step.tok_seq.data_ptr(), step.positions.data_ptr(), T, heads, kv_heads, head_dim, v_dim,
+                   cache.k.shape[0], 1 if append else 0, self.status.data_ptr(), self._stream())
+        self.launches += 1
+
+    def pool_blocks(self, cache, pooled, step, pool: int, kv_heads: int, head_dim: int, v_dim: int) -> None:
+        """The mean key and value of every block of ``pool`` tokens whose last token this step cached, from ``cache`` into
+        ``pooled`` (float32 storage whose entry e is block e)."""
+        self._dev(cache.k, cache.v, pooled.k, pooled.v)
+        if pooled.k.dtype != torch.float32 or tuple(pooled.k.shape[1:]) != (kv_heads, 64, head_dim) \
+                or tuple(pooled.v.shape[1:]) != (kv_heads, 64, v_dim) or not pooled.k.is_contiguous() or not pooled.v.is_contiguous():
+            raise KernelError("pool_blocks: the pooled store must be contiguous float32 with the cache's heads")
+        pt, pp = step.page_tables[cache.group], step.page_tables[pooled.group]
+        if pt.shape[1] != pp.shape[1]:
+            raise KernelError("pool_blocks: the two page tables differ in width")
+        self._call("hb_pool_blocks", cache.k.data_ptr(), cache.v.data_ptr(), _code(cache.k), pooled.k.data_ptr(), pooled.v.data_ptr(),
+                   pt.data_ptr(), pp.data_ptr(), pt.shape[1], step.seq_pos0.data_ptr(), step.seq_len.data_ptr(), step.num_seqs,
+                   step.max_new, int(pool), kv_heads, head_dim, v_dim, cache.k.shape[0], pooled.k.shape[0], self.status.data_ptr(),
+                   self._stream())
+        self.launches += 1
+
+    ATTENTION_POOL_TILE = 16            # query tokens of a sequence that share a block
+    ATTENTION_POOL_MAX_SPLITS = 64
+
+    def attention_pool_splits(self, step, heads: int, window: Optional[int], pool: int) -> int:
+        """Key ranges a step is cut into: one unless the step's blocks would leave most of the device idle and a
+        query sees enough keys (decode steps over long sequences)."""
+        tiles = sum(-(-n // self.ATTENTION_POOL_TILE) for n in step.host_new) * heads
+        keys = step.max_len if not window else min(step.max_len, window + step.max_new) + (step.max_len // pool if pool else 0)
+        if tiles >= self.sm_count or keys < 256:
+            return 1
+        return max(1, min(self.ATTENTION_POOL_MAX_SPLITS, self.sm_count // tiles, keys // 128))
+
+    def attention_pool(self, q, cache, pooled, step, head_bias, gate, out, heads: int, kv_heads: int, head_dim: int, v_dim: int,
+                       scale: float, window: Optional[int], pool: int, workspace=None) -> None:
+        """Attention whose weights are ``sigmoid(q . k * scale + head_bias[head])``, not normalised: a query sees the last
+        ``window`` tokens and, with ``pool``, one mean key and value (``pooled``) per block of ``pool`` tokens wholly before
+        them; the result is multiplied by ``sigmoid(gate)`` (float32 ``[tokens, heads * v_dim]``, may be None)."""
+        self._dev(q, cache.k, cache.v, head_bias, gate, out)
+        T = q.shape[0]
+        if tuple(out.shape) != (T, heads * v_dim) or tuple(q.shape) != (T, heads * head_dim):
+            raise KernelError("attention_pool: shapes do not agree")
+        if tuple(cache.k.shape[1:]) != (kv_heads, 64, head_dim) or tuple(cache.v.shape[1:]) != (kv_heads, 64, v_dim):
+            raise KernelError("attention_pool: cache layer does not match the heads")
+        if gate is not None and (gate.dtype != torch.float32 or tuple(gate.shape) != (T, heads * v_dim)):
+            raise KernelError("attention_pool: the gate must be float32 [tokens, heads * v_dim]")
+        if pool and (pooled is None or not window):
+            raise KernelError("attention_pool: pooled blocks need their store and a window")
+        pt = step.page_tables[cache.group]
+        pp = step.page_tables[pooled.group] if pool else None
+        splits = self.attention_pool_splits(step, heads, window, pool)
+        partial = None
+        if splits > 1:
+            # the same buffer for every step of a shape: a captured graph holds its address
+            partial = workspace.buffer(f"attention_pool.partial{step.tag}.{splits}", (splits, T, heads * v_dim), torch.float32)
+        tiles = sum(-(-n // self.ATTENTION_POOL_TILE) for n in step.host_new)
+        self._call("hb_attention_pool", q.data_ptr(), _code(q), _rows(q, "queries"), cache.k.data_ptr(), cache.v.data_ptr(),
+                   _code(cache.k), pooled.k.data_ptr() if pool else None, pooled.v.data_ptr() if pool else None, pt.data_ptr(),
+                   pp.data_ptr() if pool else None, pt.shape[1], step.seq_start.data_ptr(), step.seq_pos0.data_ptr(), step.num_seqs,
+                   tiles, self._f32_vec(head_bias, heads, "head bias") if head_bias is not None else None,
+                   gate.data_ptr() if gate is not None else None, _rows(gate, "gate") if gate is not None else 0, out.data_ptr(),
+                   _code(out), _rows(out, "attention output"), partial.data_ptr() if partial is not None else None, T, heads, kv_heads,
+                   head_dim, v_dim, float(scale), int(window) if window else 0, int(pool) if pool else 0, cache.k.shape[0],
+                   pooled.k.shape[0] if pool else 0, splits, self.status.data_ptr(), self._stream())
+        self.launches += 1 if splits == 1 else 2
+
+    # ------------------------------------------------------------------ matrix memory with a fixed decay
+    ACTIVATIONS = {None: 0, "none": 0, "silu": 1}
+
+    def decay_memory(self, proj, decay, state, step, out, heads: int, d: int, dv: int, activation="silu") -> None:
+        """``S <- decay[h] S + k v^T; o = S^T q`` per head over a step's tokens, sequence by sequence, with q, k, v the
+        activation of the float32 projections ``[q | k | v | ...]``; ``state`` float32 ``[slots, heads * d * dv]``, ``out``
+        float32 ``[tokens, heads * dv]``."""
+        self._dev(proj, decay, state, out)
+        T = proj.shape[0]
+        if proj.dtype != torch.float32 or out.dtype != torch.float32 or tuple(out.shape) != (T, heads * dv):
+            raise KernelError("decay_memory: float32 projections and float32 [tokens, heads * dv] output expected")
+        if state.dtype != torch.float32 or state.dim() != 2 or state.shape[1] != heads * d * dv or state.stride(1) != 1:
+            raise KernelError("decay_memory: state must be float32 [slots, heads * d * dv]")
+        self._call("hb_decay_memory", proj.data_ptr(), _rows(proj, "projections"), self._f32_vec(decay, heads, "decay"), state.data_ptr(),
+                   state.stride(0), step.state_slots.data_ptr(), step.seq_start.data_ptr(), out.data_ptr(), _rows(out, "output"),
+                   step.num_seqs, heads, d, dv, self.ACTIVATIONS[activation], self._stream())
+        self.launches += 1
+
+    def gated_norm(self, o, gate, weight, eps: float, out, out_scale: float = 1.0) -> None:
+        """``out = o / sqrt(mean(o^2) + eps) * weight * sigmoid(gate) * out_scale`` over whole rows (``gate`` may be None)."""
+        self._dev(o, gate, weight, out)
+        T, n = o.shape
+        if o.dtype != torch.float32 or tuple(out.shape) != (T, n) or (gate is not None and (gate.dtype != torch.float32 or tuple(gate.shape) != (T, n))):
+            raise KernelError("gated_norm: float32 [tokens, n] input and gate expected")
+        self._call("hb_gated_norm", o.data_ptr(), _rows(o, "gated_norm input"), gate.data_ptr() if gate is not None else None,
+                   _rows(gate, "gate") if gate is not None else 0, self._f32_vec(weight, n, "norm weight"), float(eps), float(out_scale),
+                   out.data_ptr(), _code(out), _rows(out, "gated_norm output"), T, n, self._stream())
+        self.launches += 1
+
+    # ------------------------------------------------------------------ selective state-space scan
+    def conv_act(self, x, conv_weight, conv_bias, state, step, out, activation="silu") -> None:
+        """``out[t] = act(bias + sum_j w[:, j] x[t - taps + 1 + j])`` per channel and sequence; ``x`` float32 (a column range
+        of a wider matrix is fine), ``state`` float32 ``[slots, (taps - 1) * C]``: every sequence's last inputs, brought up to date."""
+        self._dev(x, conv_weight, conv_bias, state, out)
+        T, C = x.shape
+        taps = conv_weight.shape[1]
+        if x.dtype != torch.float32 or tuple(out.shape) != (T, C) or tuple(conv_weight.shape) != (C, taps) \
+                or conv_weight.dtype != torch.float32 or not conv_weight.is_contiguous():
+            raise KernelError("conv_act: float32 input, float32 taps [channels, taps] and an output of the input's shape expected")
+        if state.dtype != torch.float32 or state.dim() != 2 or state.shape[1] != (taps - 1) * C or (taps > 1 and state.stride(1) != 1):
+            raise KernelError("conv_act: state must be float32 [slots, (taps - 1) * channels]")
+        self._call("hb_conv_act", x.data_ptr(), _rows(x, "conv_act input"), conv_weight.data_ptr(),
+                   self._f32_vec(conv_bias, C, "convolution bias") if conv_bias is not None else None, taps, state.data_ptr(),
+                   state.stride(0), step.state_slots.data_ptr(), step.seq_start.data_ptr(), out.data_ptr(), _code(out),
+                   _rows(out, "conv_act output"), step.num_seqs, step.max_new, C, self.ACTIVATIONS[activation], self._stream())
+        self.launches += 1
+
+    def selective_scan(self, u, dbc, z, w_dt, b_dt, a_log, d_skip, state, step, out, dt_rank: int, n_state: int) -> None:
+        """The selective scan over a step's tokens, sequence by sequence: ``dbc`` float32 rows ``[dt low rank | B | C]``, ``z``
+        float32 gate input, ``u`` and ``out`` in the activations' dtype ``[tokens, inner]``; ``state`` float32 ``[slots, inner * n_state]``."""
+        self._dev(u, dbc, z, w_dt, b_dt, a_log, d_skip, state, out)
+        T, inner = u.shape
+        if dbc.dtype != torch.float32 or z.dtype != torch.float32 or tuple(z.shape) != (T, inner) or tuple(out.shape) != (T, inner) \
+                or dbc.shape[0] != T or dbc.shape[1] < dt_rank + 2 * n_state or u.dtype != out.dtype:
+            raise KernelError("selective_scan: shapes or dtypes do not agree")
+        if tuple(w_dt.shape) != (inner, dt_rank) or w_dt.dtype != torch.float32 or not w_dt.is_contiguous() \
+                or tuple(a_log.shape) != (inner, n_state) or a_log.dtype != torch.float32 or not a_log.is_contiguous():
+            raise KernelError("selective_scan: float32 step-size weights [inner, dt_rank] and A_log [inner, state] expected")
+        if state.dtype != torch.float32 or state.dim() != 2 or state.shape[1] != inner * n_state or state.stride(1) != 1:
+            raise KernelError("selective_scan: state must be float32 [slots, inner * state]")
+        self._call("hb_selective_scan", u.data_ptr(), _code(u), _rows(u, "scan input"), dbc.data_ptr(), _rows(dbc, "scan parameters"),
+                   z.data_ptr(), _rows(z, "scan gate"), w_dt.data_ptr(), self._f32_vec(b_dt, inner, "step-size bias"), a_log.data_ptr(),
+                   self._f32_vec(d_skip, inner, "skip weight"), state.data_ptr(), state.stride(0), step.state_slots.data_ptr(),
+                   step.seq_start.data_ptr(), out.data_ptr(), _code(out), _rows(out, "scan output"), step.num_seqs, inner, n_state,
+                   dt_rank, self._stream())
+        self.launches += 1
+
+    # ------------------------------------------------------------------ mixture of experts
+    def moe_route(self, h, w_router, top: int, experts, weights) -> None:
+        """Per token the ``top`` experts with the largest router logits (``w_router`` float32 ``[experts, width]``, logits in
+        32-bit) into ``experts`` int32 ``[tokens, top]`` and the softmax over those logits into ``weights`` float32."""
+        self._dev(h, w_router, experts, weights)
+        T, W = h.shape
+        E = w_router.shape[0]
+        if w_router.dtype != torch.float32 or not w_router.is_contiguous() or w_router.shape[1] != W or experts.dtype != torch.int32 \
+                or weights.dtype != torch.float32 or tuple(experts.shape) != (T, top) or tuple(weights.shape) != (T, top) \
+                or not experts.is_contiguous() or not weights.is_contiguous():
+            raise KernelError("moe_route: float32 router [experts, width], int32 and float32 [tokens, top] outputs expected")
+        self._call("hb_moe_route", h.data_ptr(), _code(h), _rows(h, "router input"), w_router.data_ptr(), experts.data_ptr(),
+                   weights.data_ptr(), T, W, E, int(top), self._stream())
+        self.launches += 1
+
+    def moe_max_tiles(self, entries: int, n_experts: int) -> int:
+        return int(self.lib.hb_moe_max_tiles(int(entries), int(n_experts)))
+
+    def moe_experts(self, h, experts, weights, w_gate, w_up, w_down, limit: float, alpha: float, out, accumulate: bool, workspace,
+                    cap: int, tag: str = "") -> None:
+        """``out (+)= sum_k weights[t, k] * expert_{experts[t, k]}(h[t])`` with the experts' weights stacked ``[experts, ff,
+        width]`` (gate, up) and ``[experts, width, ff]`` (down) in the activations' dtype and the clamped gated unit of
+        ``glu_clamp`` between them.  Four launches: plan, gate/up with activation, down, weighted sum."""
+        self._dev(h, experts, weights, w_gate, w_up, w_down, out)
+        T, W = h.shape
+        E, F = w_gate.shape[0], w_gate.shape[1]
+        top = experts.shape[1]
+        if tuple(w_gate.shape) != (E, F, W) or tuple(w_up.shape) != (E, F, W) or tuple(w_down.shape) != (E, W, F) \
+                or not (w_gate.is_contiguous() and w_up.is_contiguous() and w_down.is_contiguous()) \
+                or not (w_gate.dtype == w_up.dtype == w_down.dtype == h.dtype):
+            raise KernelError("moe_experts: stacked contiguous expert weights in the activations' dtype expected")
+        if out.dtype != torch.float32 or tuple(out.shape) != (T, W):
+            raise KernelError("moe_experts: float32 [tokens, width] output expected")
+        entries = T * top
+        most = cap * top
+        max_tiles = self.moe_max_tiles(entries, E)
+        plan = workspace.buffer("moe.plan" + tag, (E + 1 + most + 1 + 2 * self.moe_max_tiles(most, E),), torch.int32)
+        offsets, order, tiles = plan[: E + 1], plan[E + 1: E + 1 + most], plan[E + 1 + most:]
+        act = workspace.buffer("moe.act" + tag, (most, F), h.dtype)
+        down = workspace.buffer("moe.down" + tag, (most, W), torch.float32)
+        s = self._stream()
+        self._call("hb_moe_plan", experts.data_ptr(), entries, E, offsets.data_ptr(), order.data_ptr(), tiles.data_ptr(), s)
+        self._call("hb_moe_glu", h.data_ptr(), _code(h), _rows(h, "expert input"), w_gate.data_ptr(), w_up.data_ptr(), _code(w_gate),
+                   offsets.data_ptr(), order.data_ptr(), tiles.data_ptr(), max_tiles, top, act.data_ptr(), _code(act), F, F, W,
+                   float(limit), float(alpha), s)
+        self._call("hb_moe_down", act.data_ptr(), _code(act), F, w_down.data_ptr(), _code(w_down), offsets.data_ptr(), order.data_ptr(),
+                   tiles.data_ptr(), max_tiles, top, down.data_ptr(), W, W, F, s)
+        self._call("hb_moe_combine", down.data_ptr(), W, weights.data_ptr(), top, out.data_ptr(), _rows(out, "expert output"), T, W,
+                   1 if accumulate else 0, s)
+        self.launches += 4
+
+    def glu_clamp(self, gate_up, out, limit: float, alpha: float) -> None:
+        """``out = g' sigmoid(alpha g') (u' + 1)`` with ``g' = min(g, limit)``, ``u' = clamp(u, -limit, limit)`` from float32 ``[g | u]``."""
+        self._dev(gate_up, out)
+        T, F = out.shape
+        if gate_up.dtype != torch.float32 or tuple(gate_up.shape) != (T, 2 * F):
+            raise KernelError("glu_clamp: float32 [rows, 2 * ff] input expected")
+        self._call("hb_glu_clamp", gate_up.data_ptr(), _rows(gate_up, "glu_clamp input"), out.data_ptr(), _code(out),
+                   _rows(out, "glu_clamp output"), T, F, float(limit), float(alpha), self._stream())
         self.launches += 1
 
     # ------------------------------------------------------------------ random weights

@@ -55,13 +55,19 @@ class ParamSpec:
 class CacheNeed:
     """Keys and values a mixer keeps per token: ``window`` None keeps all of them; with a window
     the sequence's first ``keep_first`` tokens stay visible (and stored) for good.  ``v_head_dim``:
-    the size of a value head where it differs from a key head's."""
+    the size of a value head where it differs from a key head's.  ``stride`` above 1: one key and
+    value per WHOLE run of ``stride`` tokens (entry ``e`` stands for the positions ``e * stride`` to
+    ``e * stride + stride - 1`` and exists once the sequence holds them all), which is what a mixer
+    that keeps pooled summaries of its past needs.  ``store_f32``: 32-bit storage whatever the
+    cache's dtype.  A mixer may ask for several needs at once (a tuple): it then gets a view per need."""
 
     num_kv_heads: int
     head_dim: int
     window: Optional[int] = None
     v_head_dim: Optional[int] = None
     keep_first: int = 0
+    stride: int = 1
+    store_f32: bool = False
 
     @property
     def value_dim(self) -> int:
@@ -126,9 +132,16 @@ class Mixer(Part):
     and ``prepare`` (what ``Norm.fold_request`` returned for the norm that reads ``residual``
     next: the part's last product fills that norm's buffer).  ``forward`` then returns the
     ``PreparedNorm`` for the next reader, or None when it prepared nothing (the block runs the
-    norm).  Parts without the attribute are called without the two arguments."""
+    norm).  Parts without the attribute are called without the two arguments.
+
+    A part with ``can_overwrite = True`` also takes ``accumulate=False``: it then WRITES its result
+    to ``residual`` (which is then some other 32-bit buffer of the same shape) instead of adding
+    it.  Blocks that put something between a sublayer and the residual stream (a norm on the
+    sublayer's output, a weighted sum of several mixers) use it; for other parts they zero the
+    buffer first."""
 
     folds_norms = False
+    can_overwrite = False
 
     def cache_need(self) -> Optional[CacheNeed]:
         return None
@@ -141,9 +154,10 @@ class Mixer(Part):
 
 
 class FeedForward(Part):
-    """As ``Mixer``: reads ``h``, adds to ``residual``; ``folds_norms`` as there."""
+    """As ``Mixer``: reads ``h``, adds to ``residual``; ``folds_norms`` and ``can_overwrite`` as there."""
 
     folds_norms = False
+    can_overwrite = False
 
     def forward(self, h, residual, step):
         raise NotImplementedError
@@ -171,6 +185,12 @@ class Norm(Part):
 
     def forward(self, x, out, rows=None) -> None:
         raise NotImplementedError
+
+    def add_normed(self, y, x, then=None, then_out=None) -> bool:
+        """``x += norm(y)`` for a norm that sits on a sublayer's OUTPUT (``x`` the 32-bit residual stream, ``y`` the
+        sublayer's 32-bit result).  ``then``/``then_out``: the norm that reads ``x`` next and its output buffer; a norm
+        that can make both in one pass does and returns True, else it returns False and the caller runs ``then``."""
+        raise NotImplementedError(f"{type(self).__name__} cannot sit on a sublayer's output")
 
     def fold_request(self, out):
         """What the product that writes this norm's input needs in order to prepare it

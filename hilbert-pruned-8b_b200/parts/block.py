@@ -163,3 +163,50 @@ class FilteredPreNormBlock(Block):
             self.feed_forward_norm.forward(x, h)
             self.feed_forward.forward(h, x, step)
         return None
+
+
+@BLOCKS.register("sandwich")
+class SandwichBlock(Block):
+    """Norms before AND after each sublayer: ``x += post_a(mixer(norm_a(x)))``, then, if the layer has a
+    feed-forward, ``x += post_b(feed_forward(norm_b(x)))``.  A sublayer writes its result to a 32-bit buffer
+    of the residual stream's shape (parts with ``can_overwrite`` write it, for others the buffer is zeroed and
+    they add); the norm on the output adds it to the stream (``Norm.add_normed``) and, where it can, makes
+    the next sublayer's input in the same pass."""
+
+    ROLES = {"mixer_norm": NORMS, "mixer": MIXERS, "mixer_post_norm": NORMS, "feed_forward_norm": NORMS,
+             "feed_forward": FEED_FORWARDS, "feed_forward_post_norm": NORMS}
+    OPTIONAL = ("feed_forward_norm", "feed_forward", "feed_forward_post_norm")
+
+    def __init__(self, layer_spec, ctx):
+        super().__init__(layer_spec, ctx)
+        p = self.parts
+        self.mixer_norm, self.mixer, self.mixer_post = p["mixer_norm"], p["mixer"], p["mixer_post_norm"]
+        self.ff_norm, self.ff, self.ff_post = p.get("feed_forward_norm"), p.get("feed_forward"), p.get("feed_forward_post_norm")
+        if len({self.ff_norm is None, self.ff is None, self.ff_post is None}) != 1:
+            raise ValueError(f"layer {layer_spec.prefix!r}: a feed-forward and its two norms come together")
+        self.fuse_norms = True              # tests switch it off to run the two norms between the sublayers one by one
+
+    @staticmethod
+    def _run(part, y, args):
+        if getattr(part, "can_overwrite", False):
+            part.forward(*args, accumulate=False)
+        else:
+            y.zero_()
+            part.forward(*args)
+
+    def forward(self, x, step, cache, state, append: bool):
+        ws, cap, T = self.ctx.workspace, self.ctx.max_step_tokens, step.num_tokens
+        h = ws.buffer("block.h", (cap, x.shape[1]), self.ctx.dtype)[:T]
+        y = ws.buffer("block.branch", (cap, x.shape[1]), torch.float32)[:T]
+        self.mixer_norm.forward(x, h)
+        self._run(self.mixer, y, (h, y, step, cache, state, append))
+        if self.ff is None:
+            self.mixer_post.add_normed(y, x)
+            return None
+        if not (self.fuse_norms and self.mixer_post.add_normed(y, x, then=self.ff_norm, then_out=h)):
+            if not self.fuse_norms:
+                self.mixer_post.add_normed(y, x)
+            self.ff_norm.forward(x, h)
+        self._run(self.ff, y, (h, y, step))
+        self.ff_post.add_normed(y, x)
+        return None

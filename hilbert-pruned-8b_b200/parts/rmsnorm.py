@@ -21,14 +21,15 @@ class RMSNorm(Norm):
         self.size = int(spec.params["size"])
         self.eps = float(spec.params["eps"])
         self.offset = float(spec.get("offset", 0.0))
+        self.tensor_name = spec.get("tensor_name", "weight")     # below the part's prefix ("": the prefix itself)
         self.weight = None
 
     def params(self) -> List[ParamSpec]:
-        return [ParamSpec("weight", (self.size,), kind="vector", init="ones")]
+        return [ParamSpec(self.tensor_name, (self.size,), kind="vector", init="ones")]
 
     def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
         # widened once at load, exactly (model.c:259-281)
-        self.weight = tensors["weight"].reshape(self.size).to(torch.float32).contiguous()
+        self.weight = tensors[self.tensor_name].reshape(self.size).to(torch.float32).contiguous()
 
     def weight_bytes(self) -> int:
         return self.size * 4
@@ -39,3 +40,11 @@ class RMSNorm(Norm):
 
     def fold_request(self, out):
         return (self.weight, self.offset, self.eps, out)
+
+    def add_normed(self, y, x, then=None, then_out=None) -> bool:
+        """``x += norm(y)``; with ``then`` (the norm that reads ``x`` next, if it is an RMSNorm too) also
+        ``then_out = then(x)`` in the same pass.  Returns whether ``then_out`` was written."""
+        fuse = isinstance(then, RMSNorm) and then_out is not None and then.size == self.size
+        self.ctx.ops.rmsnorm_add(y, self.weight, self.eps, self.offset, x, (then.weight, then.eps, then.offset) if fuse else None,
+                                 then_out if fuse else None)
+        return fuse

@@ -100,7 +100,9 @@ class SinkAttention(Mixer):
         return CacheNeed(self.kv_heads, self.head_dim, self.window, v_head_dim=self.v_dim,
                          keep_first=self.keep_first if self.window is not None else 0)
 
-    def forward(self, h, residual, step, cache, state, append: bool):
+    can_overwrite = True        # forward(..., accumulate=False) writes its result instead of adding it
+
+    def forward(self, h, residual, step, cache, state, append: bool, accumulate: bool = True):
         ops, ws, T, cap = self.ctx.ops, self.ctx.workspace, step.num_tokens, self.ctx.max_step_tokens
         H, G, d, dv = self.heads, self.kv_heads, self.head_dim, self.v_dim
         proj = ws.buffer("sink_attention.proj", (cap, self.proj_ld), torch.float32)[:T]
@@ -159,4 +161,4 @@ class SinkAttention(Mixer):
             partial = ws.buffer("sink_attention.partial_general", (cap, H * n_val * dv), torch.float32)[:T]
             ops.attention_sink(q, H, G, d, dv, cache, step, partial, self.scale, self.window, self.keep_first, all_values)
             ops.head_mix(partial, self.talk_matrix, attn, H, G, dv, n_val, ones)
-        ops.linear(attn, self.w_o, residual, accumulate=True)
+        ops.linear(attn, self.w_o, residual, accumulate=accumulate)

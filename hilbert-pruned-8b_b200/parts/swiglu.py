@@ -19,32 +19,35 @@ class SwiGLU(FeedForward):
         super().__init__(spec, ctx)
         self.hidden = int(spec.params["hidden_size"])
         self.inter = int(spec.params["intermediate_size"])
+        # the tensors' names below the part's prefix: (gate, up, down)
+        self.names = tuple(spec.get("tensor_names", ("gate_proj.weight", "up_proj.weight", "down_proj.weight")))
         self.w_gate_up = None
         self.w_down = None
 
     def params(self) -> List[ParamSpec]:
         return [
-            ParamSpec("gate_proj.weight", (self.inter, self.hidden)),
-            ParamSpec("up_proj.weight", (self.inter, self.hidden)),
-            ParamSpec("down_proj.weight", (self.hidden, self.inter)),
+            ParamSpec(self.names[0], (self.inter, self.hidden)),
+            ParamSpec(self.names[1], (self.inter, self.hidden)),
+            ParamSpec(self.names[2], (self.hidden, self.inter)),
         ]
 
     def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
-        g, u = tensors["gate_proj.weight"], tensors["up_proj.weight"]
+        g, u = tensors[self.names[0]], tensors[self.names[1]]
         if g.dtype != u.dtype:
             raise ValueError("swiglu: gate and up projections are stored in different dtypes")
         pack = self.ctx.ops.pack_weight
         self.w_gate_up = pack(torch.cat([g, u], dim=0).contiguous(), swiglu=True)
-        self.w_down = pack(tensors["down_proj.weight"].contiguous())
+        self.w_down = pack(tensors[self.names[2]].contiguous())
 
     def weight_bytes(self) -> int:
         return sum(w.numel() * w.element_size() for w in (self.w_gate_up, self.w_down))
 
     folds_norms = True
+    can_overwrite = True        # forward(..., accumulate=False) writes its result instead of adding it
 
-    def forward(self, h, residual, step, prepared=None, prepare=None):
+    def forward(self, h, residual, step, prepared=None, prepare=None, accumulate: bool = True):
         ops, ws, T = self.ctx.ops, self.ctx.workspace, step.num_tokens
         cap = self.ctx.max_step_tokens
         act = ws.buffer("swiglu.act", (cap, self.inter), self.ctx.dtype)[:T]
         ops.linear_swiglu(h, self.w_gate_up, act, ws, cap, scale=prepared)
-        return ops.linear(act, self.w_down, residual, accumulate=True, prepare=prepare)
+        return ops.linear(act, self.w_down, residual, accumulate=accumulate, prepare=prepare if accumulate else None)
