@@ -4,6 +4,7 @@
     python bench.py --workload 3b|1b      # a line of its own: unequal prompts, then decoding
     python bench.py --timeline --layers 3 --skip-points    # per-kernel times inside the decode graph
     python bench.py --design pogezen      # a line of its own: the Pogezen design beside Llama layers of equal size
+    python bench.py --design vuladra      # a line of its own: the Vuladra design beside Pogezen layers of equal size
 
 Prints ONE JSON line.  A step is one decode step of a batch of 8 sequences whose caches hold
 about 8192 tokens each; ``value`` is decoded tokens per second from CUDA events around the
@@ -420,6 +421,32 @@ def pogezen_config(z):
             "layers": [dict(att, mlp=mlp), dict(rec, mlp=None), dict(att, mlp=mlp), dict(rec, mlp=mlp)]}
 
 
+# --design vuladra: four Vuladra layers (selective scan + dense feed-forward; attention over a window and pooled blocks +
+# mixture of experts; softmax window attention beside a decayed matrix memory + mixture of experts; selective scan +
+# mixture of experts) beside the four Pogezen layers above, the library's closest model (windowed attention, a recurrent
+# matrix memory, feed-forwards), at the same width, heads, head size and window.  The scan has twice the width as inner
+# size, 16 state values and step sizes of rank width / 16; the experts are 16 of a quarter of the dense feed-forward's size,
+# two chosen, with a shared expert of that size.
+VULADRA_POOL, VULADRA_EXPERTS, VULADRA_TOP = 64, 16, 2
+
+
+def vuladra_config(z):
+    W, hd = z["width"], z["head_dim"]
+    scan = {"type": "mamba1", "mixer": {"inner": 2 * W, "state": 16, "dt_rank": W // 16, "conv": 4}}
+    att = {"type": "attention", "mixer": {"heads": z["heads"], "kv_heads": z["kv"], "dim": hd, "vdim": hd, "scale": hd ** -0.5,
+                                          "mask": {"size": DESIGN_WINDOW, "pool": VULADRA_POOL}}}
+    par = {"type": "parallel", "mixer": {
+        "left": {"heads": z["heads"], "kv_heads": z["kv"], "dim": hd, "vdim": hd, "scale": hd ** -0.5, "mask": {"size": DESIGN_WINDOW}},
+        "right": {"heads": z["ml_heads"], "dim": z["ml_dim"], "vdim": W // z["ml_heads"],
+                  "decay": [1.0 - 2.0 ** -(3 + i) for i in range(z["ml_heads"])]},
+        "left_scale": 1.0, "right_scale": 1.0}}
+    dense = {"kind": "dense", "ff": z["ff"]}
+    moe = {"kind": "moe", "router": {"experts": VULADRA_EXPERTS, "top": VULADRA_TOP}, "expert": {"ff": z["ff"] // 4, "limit": 7.0},
+           "shared": {"ff": z["ff"] // 4, "limit": 7.0}}
+    return {"architecture": "Vuladra", "norm": {"eps": 1e-6}, "vocab": DESIGN_VOCAB, "width": W,
+            "layers": [dict(scan, mlp=dense), dict(att, mlp=moe), dict(par, mlp=moe), dict(scan, mlp=moe)]}
+
+
 def llama_like_config(z):
     return dict(MODEL_8B, hidden_size=z["width"], num_hidden_layers=4, intermediate_size=z["ff"], vocab_size=DESIGN_VOCAB,
                 num_attention_heads=z["heads"], num_key_value_heads=z["kv"], head_dim=z["head_dim"], tie_word_embeddings=True)
@@ -468,8 +495,11 @@ def design_comparison(a) -> int:
     out = {}
     for size, z in DESIGN_SIZES.items():
         row = {}
-        for who, cfg in (("pogezen", hb.PogezenConfig.from_dict(pogezen_config(z))),
-                         ("llama", hb.LlamaConfig.from_dict(llama_like_config(z)))):
+        if a.design == "vuladra":
+            pair = (("vuladra", hb.VuladraConfig.from_dict(vuladra_config(z))), ("pogezen", hb.PogezenConfig.from_dict(pogezen_config(z))))
+        else:
+            pair = (("pogezen", hb.PogezenConfig.from_dict(pogezen_config(z))), ("llama", hb.LlamaConfig.from_dict(llama_like_config(z))))
+        for who, cfg in pair:
             llm = LLM.random(cfg, seed=0, dtype="bfloat16", max_tokens=batch * (context + 128) + 2 * prompt, device=0,
                              max_batch=batch, max_step_tokens=prompt)
             fill_cache_random(llm)
@@ -500,7 +530,8 @@ def design_comparison(a) -> int:
             del llm, eng, seqs
             torch.cuda.empty_cache()
         out[size] = row
-    print(json.dumps({"metric": "Pogezen layers beside Llama layers of equal size: prefill of one 2048-token prompt and decode "
+    names = "Vuladra layers beside Pogezen layers" if a.design == "vuladra" else "Pogezen layers beside Llama layers"
+    print(json.dumps({"metric": f"{names} of equal size: prefill of one 2048-token prompt and decode "
                                 f"steps of batch {batch} at context {context}, four layers, random weights",
                       "unit": "tokens/s", "dtype": "bf16", "n_gpus": 1, "steps": a.steps, "warmup": a.warmup,
                       "config": {"window": DESIGN_WINDOW, "keep_first": DESIGN_KEEP, "vocab": DESIGN_VOCAB, "sizes": DESIGN_SIZES,
@@ -603,7 +634,7 @@ def main() -> int:
     ap.add_argument("--skip-points", action="store_true")
     ap.add_argument("--workload", choices=("8b", "3b", "1b"), default="8b",
                     help="8b: the default line; 3b, 1b: the generation workloads at those shapes (--steps = repeats)")
-    ap.add_argument("--design", choices=("pogezen",), default=None,
+    ap.add_argument("--design", choices=("pogezen", "vuladra"), default=None,
                     help="a line of its own: this design's layers beside Llama layers of equal size (prefill, decode, "
                          "device time per kernel); the default workload is not run")
     ap.add_argument("--timeline", action="store_true",

@@ -194,13 +194,16 @@ int hb_selective_scan(const void* u, int u_dtype, long long ldu, const float* db
 // Mixture of experts (moe.cu)
 int hb_moe_route(const void* h, int h_dtype, long long ldh, const float* w_router, int* experts, float* weights, int n_tokens, int width,
                  int n_experts, int top, void* stream);
-int hb_moe_plan(const int* experts, int n_entries, int n_experts, int* offsets, int* order, int* tiles, void* stream);
-int hb_moe_max_tiles(int n_entries, int n_experts);
+// tile_rows: hb_moe_tile_rows(tensor_cores), the rows of a plan tile of the products' variant (FP32 pipe, or mma.sync for
+// bfloat16 operands whose rows are multiples of 8 elements)
+int hb_moe_tile_rows(int tensor_cores);
+int hb_moe_plan(const int* experts, int n_entries, int n_experts, int tile_rows, int* offsets, int* order, int* tiles, void* stream);
+int hb_moe_max_tiles(int n_entries, int n_experts, int tile_rows);
 int hb_moe_glu(const void* h, int h_dtype, long long ldh, const void* w_gate, const void* w_up, int w_dtype, const int* offsets,
                const int* order, const int* tiles, int max_tiles, int top, void* act, int act_dtype, long long lda, int ff, int width,
-               float limit, float alpha, void* stream);
+               float limit, float alpha, int tensor_cores, void* stream);
 int hb_moe_down(const void* act, int act_dtype, long long lda, const void* w_down, int w_dtype, const int* offsets, const int* order,
-                const int* tiles, int max_tiles, int top, float* down, long long ldd, int width, int ff, void* stream);
+                const int* tiles, int max_tiles, int top, float* down, long long ldd, int width, int ff, int tensor_cores, void* stream);
 int hb_moe_combine(const float* down, long long ldd, const float* weights, int top, float* out, long long ldo, int n_tokens, int width,
                    int accumulate, void* stream);
 int hb_glu_clamp(const float* in, long long ldi, void* out, int out_dtype, long long ldo, int n_rows, int F, float limit, float alpha,

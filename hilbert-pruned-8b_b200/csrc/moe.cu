@@ -20,11 +20,18 @@
 // [gate | up] matrix (a shared expert, whose products are ordinary matrix products).
 #include "api.h"
 #include "common.cuh"
+#include "mma.cuh"
 
 #define MOE_BM 32
 #define MOE_BN 32
 #define MOE_BK 32
 #define MOE_THREADS 256
+// the tensor-core variant (bfloat16, rows of a multiple of 8 elements): MM_BM rows x MM_BN columns x MM_BK per stage
+#define MM_BM 64
+#define MM_BN 64
+#define MM_BK 64
+#define MM_STAGES 3
+#define MM_THREADS 256
 
 // ------------------------------------------------------------------------------------------------ route
 template <typename TH>
@@ -98,7 +105,7 @@ extern "C" int hb_moe_route(const void* h, int h_dtype, long long ldh, const flo
 // ------------------------------------------------------------------------------------------------ plan
 // offsets [E + 1], order [entries], tiles [1 + 2 * max_tiles]: tiles[0] = number of tiles, then (expert, first row) pairs
 __global__ void __launch_bounds__(1024)
-moe_plan_kernel(const int* __restrict__ experts, int n_entries, int E, int* __restrict__ offsets, int* __restrict__ order,
+moe_plan_kernel(const int* __restrict__ experts, int n_entries, int E, int tile_rows, int* __restrict__ offsets, int* __restrict__ order,
                 int* __restrict__ tiles) {
     pdl_trigger();
     pdl_wait();
@@ -116,7 +123,7 @@ moe_plan_kernel(const int* __restrict__ experts, int n_entries, int E, int* __re
         for (int e = 0; e < E; e++) {
             offsets[e] = at;
             cursor[e] = at;
-            for (int r = 0; r < count[e]; r += MOE_BM) {
+            for (int r = 0; r < count[e]; r += tile_rows) {
                 tiles[1 + 2 * nt] = e;
                 tiles[2 + 2 * nt] = at + r;
                 nt++;
@@ -130,15 +137,18 @@ moe_plan_kernel(const int* __restrict__ experts, int n_entries, int E, int* __re
     for (int i = tid; i < n_entries; i += 1024) order[atomicAdd(&cursor[experts[i]], 1)] = i;
 }
 
-extern "C" int hb_moe_plan(const int* experts, int n_entries, int n_experts, int* offsets, int* order, int* tiles, void* stream) {
+extern "C" int hb_moe_tile_rows(int tensor_cores) { return tensor_cores ? MM_BM : MOE_BM; }
+
+extern "C" int hb_moe_plan(const int* experts, int n_entries, int n_experts, int tile_rows, int* offsets, int* order, int* tiles, void* stream) {
     if (n_entries == 0) return 0;
     HB_REQUIRE(n_entries > 0 && n_experts > 0 && n_experts <= 4096, "moe_plan: bad sizes");
-    hb_launch(moe_plan_kernel, dim3(1), dim3(1024), sizeof(int) * 2 * n_experts, (cudaStream_t)stream, experts, n_entries, n_experts, offsets,
-              order, tiles);
+    HB_REQUIRE(tile_rows == MOE_BM || tile_rows == MM_BM, "moe_plan: tiles of %d rows (%d or %d are built)", tile_rows, MOE_BM, MM_BM);
+    hb_launch(moe_plan_kernel, dim3(1), dim3(1024), sizeof(int) * 2 * n_experts, (cudaStream_t)stream, experts, n_entries, n_experts, tile_rows,
+              offsets, order, tiles);
     return hb_check_launch("moe_plan");
 }
 
-extern "C" int hb_moe_max_tiles(int n_entries, int n_experts) { return (n_entries + MOE_BM - 1) / MOE_BM + n_experts; }
+extern "C" int hb_moe_max_tiles(int n_entries, int n_experts, int tile_rows) { return (n_entries + tile_rows - 1) / tile_rows + n_experts; }
 
 // ------------------------------------------------------------------------------------------------ the experts' products
 __device__ __forceinline__ float moe_glu(float g, float u, float limit, float alpha) {
@@ -225,13 +235,154 @@ moe_product_kernel(const TA* __restrict__ a, long long lda, const TW* __restrict
     }
 }
 
+
+// The same two products on the tensor cores (mma.sync m16n8k16, bfloat16 operands, 32-bit accumulators): a block owns a
+// plan tile of MM_BM rows and MM_BN output columns; rows (gathered by the plan's order) and weight rows arrive through a
+// MM_STAGES-deep cp.async pipeline into XOR-swizzled shared memory and are read with ldmatrix; eight warps as 4 (rows) x 2
+// (columns), each 16 rows x 32 columns (and both matrices for the gated unit, whose activation is the epilogue).
+template <bool GLU, typename TO>
+__global__ void __launch_bounds__(MM_THREADS)
+moe_product_mma_kernel(const bf16* __restrict__ a, long long lda, const bf16* __restrict__ w0, const bf16* __restrict__ w1,
+                       const int* __restrict__ offsets, const int* __restrict__ order, const int* __restrict__ tiles, int top,
+                       TO* __restrict__ out, long long ldo, int N, int K, float limit, float alpha) {
+    pdl_trigger();
+    extern __shared__ __align__(128) unsigned char mm_smem[];
+    constexpr int TILE_BYTES = MM_BM * MM_BK * 2, MATS = GLU ? 3 : 2, STAGE_BYTES = TILE_BYTES * MATS;
+    static_assert(MM_BM == MM_BN && MM_BK * 2 == 128, "one tile shape and 128-byte rows for rows and weights");
+    __shared__ int row_src[MM_BM], row_dst[MM_BM];
+    pdl_wait();
+    a = pdl_fresh(a);
+    tiles = pdl_fresh(tiles);
+    order = pdl_fresh(order);
+    offsets = pdl_fresh(offsets);
+    if ((int)blockIdx.x >= tiles[0]) return;
+    const int e = tiles[1 + 2 * blockIdx.x], r0 = tiles[2 + 2 * blockIdx.x];
+    const int rows = min(MM_BM, offsets[e + 1] - r0);
+    const int n0 = blockIdx.y * MM_BN;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    if (tid < MM_BM) {
+        const int entry = tid < rows ? order[r0 + tid] : -1;
+        row_src[tid] = entry < 0 ? -1 : (GLU ? entry / top : r0 + tid);
+        row_dst[tid] = entry < 0 ? -1 : (GLU ? r0 + tid : entry);
+    }
+    __syncthreads();
+    const bf16* we0 = w0 + (size_t)e * N * K;
+    const bf16* we1 = GLU ? w1 + (size_t)e * N * K : nullptr;
+    const uint32_t smem0 = (uint32_t)__cvta_generic_to_shared(mm_smem);
+    const int nk = (K + MM_BK - 1) / MM_BK;
+
+    auto load_stage = [&](int stage, int kb) {
+        const uint32_t base = smem0 + stage * STAGE_BYTES;
+        unsigned char* gbase = mm_smem + stage * STAGE_BYTES;
+        for (int i = tid; i < MM_BM * 8; i += MM_THREADS) {
+            const int row = i >> 3, ch = i & 7;
+            const int k = kb * MM_BK + ch * 8;
+            const uint32_t off = swizzled<128>(row, ch);
+            const int src = row_src[row];
+            if (src >= 0 && k < K) cp_async_16(base + off, a + (size_t)src * lda + k);
+            else *reinterpret_cast<uint4*>(gbase + off) = make_uint4(0u, 0u, 0u, 0u);
+            const int n = n0 + row;
+            if (n < N && k < K) {
+                cp_async_16(base + TILE_BYTES + off, we0 + (size_t)n * K + k);
+                if (GLU) cp_async_16(base + 2 * TILE_BYTES + off, we1 + (size_t)n * K + k);
+            } else {
+                *reinterpret_cast<uint4*>(gbase + TILE_BYTES + off) = make_uint4(0u, 0u, 0u, 0u);
+                if (GLU) *reinterpret_cast<uint4*>(gbase + 2 * TILE_BYTES + off) = make_uint4(0u, 0u, 0u, 0u);
+            }
+        }
+    };
+
+    const int wm = warp & 3, wn = warp >> 2;
+    float acc0[4][4], acc1[GLU ? 4 : 1][4];
+#pragma unroll
+    for (int i = 0; i < 4; i++)
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            acc0[i][j] = 0.0f;
+            if (GLU) acc1[i][j] = 0.0f;
+        }
+#pragma unroll
+    for (int s = 0; s < MM_STAGES - 1; s++) {
+        if (s < nk) load_stage(s, s);
+        cp_async_commit();
+    }
+    for (int kb = 0; kb < nk; kb++) {
+        cp_async_wait<MM_STAGES - 2>();
+        __syncthreads();                                   // stage kb has landed for everyone; stage kb - 1 has been read by everyone
+        const int nxt = kb + MM_STAGES - 1;
+        if (nxt < nk) load_stage(nxt % MM_STAGES, nxt);
+        cp_async_commit();
+        const uint32_t sa = smem0 + (kb % MM_STAGES) * STAGE_BYTES, sb0 = sa + TILE_BYTES, sb1 = sa + 2 * TILE_BYTES;
+#pragma unroll
+        for (int ks = 0; ks < MM_BK / 16; ks++) {
+            uint32_t af[4];
+            ldmatrix_x4(af, sa + swizzled<128>(wm * 16 + (lane & 15), 2 * ks + (lane >> 4)));
+#pragma unroll
+            for (int half = 0; half < 2; half++) {
+                const int brow = wn * 32 + half * 16 + ((lane >> 4) << 3) + (lane & 7);
+                const int bch = 2 * ks + ((lane >> 3) & 1);
+                uint32_t bf[4];
+                ldmatrix_x4(bf, sb0 + swizzled<128>(brow, bch));
+                mma_bf16_16816(acc0[2 * half], af, bf[0], bf[1]);
+                mma_bf16_16816(acc0[2 * half + 1], af, bf[2], bf[3]);
+                if (GLU) {
+                    ldmatrix_x4(bf, sb1 + swizzled<128>(brow, bch));
+                    mma_bf16_16816(acc1[2 * half], af, bf[0], bf[1]);
+                    mma_bf16_16816(acc1[2 * half + 1], af, bf[2], bf[3]);
+                }
+            }
+        }
+    }
+    cp_async_wait<0>();
+    const int g = lane >> 2, tg = lane & 3;
+#pragma unroll
+    for (int hr = 0; hr < 2; hr++) {
+        const int dst = row_dst[wm * 16 + g + 8 * hr];
+        if (dst < 0) continue;
+#pragma unroll
+        for (int nt = 0; nt < 4; nt++)
+#pragma unroll
+            for (int j = 0; j < 2; j++) {
+                const int n = n0 + wn * 32 + nt * 8 + 2 * tg + j;
+                if (n >= N) continue;
+                const float v0 = acc0[nt][2 * hr + j];
+                out[(size_t)dst * ldo + n] = from_f32<TO>(GLU ? moe_glu(v0, acc1[GLU ? nt : 0][2 * hr + j], limit, alpha) : v0);
+            }
+    }
+}
+
+template <bool GLU, typename TO>
+static int moe_mma_launch(dim3 grid, cudaStream_t s, const bf16* a, long long lda, const bf16* w0, const bf16* w1, const int* offsets,
+                          const int* order, const int* tiles, int top, TO* out, long long ldo, int N, int K, float limit, float alpha) {
+    constexpr int SMEM = MM_STAGES * MM_BM * MM_BK * 2 * (GLU ? 3 : 2);
+    static bool done[HB_MAX_DEVICES] = {};
+    const int slot = hb_device_slot();
+    if (!done[slot]) {
+        cudaError_t e = cudaFuncSetAttribute(moe_product_mma_kernel<GLU, TO>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+        if (e != cudaSuccess) return hb_fail("moe: shared memory: %s", cudaGetErrorString(e));
+        done[slot] = true;
+    }
+    hb_launch(moe_product_mma_kernel<GLU, TO>, dim3(grid), dim3(MM_THREADS), SMEM, s, a, lda, w0, w1, offsets, order, tiles, top, out, ldo, N, K,
+              limit, alpha);
+    return 0;
+}
+
 extern "C" int hb_moe_glu(const void* h, int h_dtype, long long ldh, const void* w_gate, const void* w_up, int w_dtype, const int* offsets,
                           const int* order, const int* tiles, int max_tiles, int top, void* act, int act_dtype, long long lda, int ff,
-                          int width, float limit, float alpha, void* stream) {
+                          int width, float limit, float alpha, int tensor_cores, void* stream) {
     HB_REQUIRE(max_tiles > 0 && ff > 0 && width > 0 && top >= 1, "moe_glu: bad sizes");
     HB_REQUIRE((ff + MOE_BN - 1) / MOE_BN <= 65535, "moe_glu: too many columns");
     dim3 grid(max_tiles, (ff + MOE_BN - 1) / MOE_BN);
     cudaStream_t s = (cudaStream_t)stream;
+    if (tensor_cores) {
+        HB_REQUIRE(h_dtype == HB_BF16 && w_dtype == HB_BF16 && act_dtype == HB_BF16 && width % 8 == 0 && ldh % 8 == 0 &&
+                   (((uintptr_t)h | (uintptr_t)w_gate | (uintptr_t)w_up) & 15) == 0,
+                   "moe_glu: the tensor-core variant needs bfloat16 operands with 16-byte aligned rows");
+        grid.y = (ff + MM_BN - 1) / MM_BN;
+        if (moe_mma_launch<true, bf16>(grid, s, (const bf16*)h, ldh, (const bf16*)w_gate, (const bf16*)w_up, offsets, order, tiles, top,
+                                       (bf16*)act, lda, ff, width, limit, alpha)) return 1;
+        return hb_check_launch("moe_glu");
+    }
     if (h_dtype == HB_BF16 && w_dtype == HB_BF16 && act_dtype == HB_BF16)
         hb_launch(moe_product_kernel<bf16, bf16, bf16, true>, dim3(grid), dim3(MOE_THREADS), 0, s, (const bf16*)h, ldh, (const bf16*)w_gate,
                   (const bf16*)w_up, offsets, order, tiles, top, (bf16*)act, lda, ff, width, limit, alpha);
@@ -243,11 +394,20 @@ extern "C" int hb_moe_glu(const void* h, int h_dtype, long long ldh, const void*
 }
 
 extern "C" int hb_moe_down(const void* act, int act_dtype, long long lda, const void* w_down, int w_dtype, const int* offsets, const int* order,
-                           const int* tiles, int max_tiles, int top, float* down, long long ldd, int width, int ff, void* stream) {
+                           const int* tiles, int max_tiles, int top, float* down, long long ldd, int width, int ff, int tensor_cores,
+                           void* stream) {
     HB_REQUIRE(max_tiles > 0 && ff > 0 && width > 0, "moe_down: bad sizes");
     HB_REQUIRE((width + MOE_BN - 1) / MOE_BN <= 65535, "moe_down: too many columns");
     dim3 grid(max_tiles, (width + MOE_BN - 1) / MOE_BN);
     cudaStream_t s = (cudaStream_t)stream;
+    if (tensor_cores) {
+        HB_REQUIRE(act_dtype == HB_BF16 && w_dtype == HB_BF16 && ff % 8 == 0 && lda % 8 == 0 && (((uintptr_t)act | (uintptr_t)w_down) & 15) == 0,
+                   "moe_down: the tensor-core variant needs bfloat16 operands with 16-byte aligned rows");
+        grid.y = (width + MM_BN - 1) / MM_BN;
+        if (moe_mma_launch<false, float>(grid, s, (const bf16*)act, lda, (const bf16*)w_down, (const bf16*)nullptr, offsets, order, tiles, top,
+                                         down, ldd, width, ff, 0.0f, 0.0f)) return 1;
+        return hb_check_launch("moe_down");
+    }
     if (act_dtype == HB_BF16 && w_dtype == HB_BF16)
         hb_launch(moe_product_kernel<bf16, bf16, float, false>, dim3(grid), dim3(MOE_THREADS), 0, s, (const bf16*)act, lda, (const bf16*)w_down,
                   (const bf16*)nullptr, offsets, order, tiles, top, down, ldd, width, ff, 0.0f, 0.0f);

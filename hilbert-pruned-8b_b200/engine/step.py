@@ -342,5 +342,10 @@ class Engine:
     def decode_step_bytes(self, live_lengths: Seq[int]) -> int:
         """Bytes a decode step has to read: every weight it uses once and the cache of the
         live sequences."""
-        kv = sum(int(l) for l in live_lengths) * self.cache.bytes_per_token()
+        es = torch.empty((), dtype=self.dtype).element_size()
+        kv = 0
+        for g in self.cache.groups:
+            # a windowed group is read as far back as its window (and its kept first tokens) only
+            reach = None if g.need.window is None else g.need.window + g.need.keep_first
+            kv += sum(int(l) if reach is None else min(int(l), reach) for l in live_lengths) * g.bytes_per_token(es)
         return self.model.step_weight_bytes() + kv

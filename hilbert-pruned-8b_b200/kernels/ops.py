@@ -93,10 +93,11 @@ _SIGNATURES = {
     "hb_selective_scan": [_c_ptr, _c_int, _c_ll, _c_ptr, _c_ll, _c_ptr, _c_ll, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ll, _c_ptr, _c_ptr,
                           _c_ptr, _c_int, _c_ll, _c_int, _c_int, _c_int, _c_int, _c_ptr],
     "hb_moe_route": [_c_ptr, _c_int, _c_ll, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_ptr],
-    "hb_moe_plan": [_c_ptr, _c_int, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_ptr],
+    "hb_moe_plan": [_c_ptr, _c_int, _c_int, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_ptr],
     "hb_moe_glu": [_c_ptr, _c_int, _c_ll, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_ptr, _c_int, _c_ll, _c_int,
-                   _c_int, _c_float, _c_float, _c_ptr],
-    "hb_moe_down": [_c_ptr, _c_int, _c_ll, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_ptr, _c_ll, _c_int, _c_int, _c_ptr],
+                   _c_int, _c_float, _c_float, _c_int, _c_ptr],
+    "hb_moe_down": [_c_ptr, _c_int, _c_ll, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_ptr, _c_ll, _c_int, _c_int, _c_int,
+                    _c_ptr],
     "hb_moe_combine": [_c_ptr, _c_ll, _c_ptr, _c_int, _c_ptr, _c_ll, _c_int, _c_int, _c_int, _c_ptr],
     "hb_glu_clamp": [_c_ptr, _c_ll, _c_ptr, _c_int, _c_ll, _c_int, _c_int, _c_float, _c_float, _c_ptr],
 }
@@ -134,7 +135,8 @@ def load_library():
         lib.hb_attention_heads_variant.argtypes, lib.hb_attention_heads_variant.restype = [_c_int] * 6, _c_int
         lib.hb_attention_heads_writes_output.argtypes, lib.hb_attention_heads_writes_output.restype = [_c_int] * 6, _c_int
         lib.hb_attention_pool_supported.argtypes, lib.hb_attention_pool_supported.restype = [_c_int] * 2, _c_int
-        lib.hb_moe_max_tiles.argtypes, lib.hb_moe_max_tiles.restype = [_c_int] * 2, _c_int
+        lib.hb_moe_max_tiles.argtypes, lib.hb_moe_max_tiles.restype = [_c_int] * 3, _c_int
+        lib.hb_moe_tile_rows.argtypes, lib.hb_moe_tile_rows.restype = [_c_int], _c_int
         lib.hb_attention_decode_ctas_per_sm.argtypes, lib.hb_attention_decode_ctas_per_sm.restype = [_c_int], _c_int
         lib.hb_attention_decode_scratch_floats.argtypes = [_c_int, _c_int, _c_int, _c_int]
         lib.hb_attention_decode_scratch_floats.restype = _c_ll
@@ -1163,14 +1165,15 @@ class Ops:
                    weights.data_ptr(), T, W, E, int(top), self._stream())
         self.launches += 1
 
-    def moe_max_tiles(self, entries: int, n_experts: int) -> int:
-        return int(self.lib.hb_moe_max_tiles(int(entries), int(n_experts)))
+    def moe_max_tiles(self, entries: int, n_experts: int, tile_rows: int) -> int:
+        return int(self.lib.hb_moe_max_tiles(int(entries), int(n_experts), int(tile_rows)))
 
     def moe_experts(self, h, experts, weights, w_gate, w_up, w_down, limit: float, alpha: float, out, accumulate: bool, workspace,
                     cap: int, tag: str = "") -> None:
         """``out (+)= sum_k weights[t, k] * expert_{experts[t, k]}(h[t])`` with the experts' weights stacked ``[experts, ff,
         width]`` (gate, up) and ``[experts, width, ff]`` (down) in the activations' dtype and the clamped gated unit of
-        ``glu_clamp`` between them.  Four launches: plan, gate/up with activation, down, weighted sum."""
+        ``glu_clamp`` between them.  Four launches: plan, gate/up with activation, down, weighted sum.  bfloat16 operands whose
+        rows are multiples of 8 elements run the products on the tensor cores (``use_tensor_cores``), all others on the FP32 pipe."""
         self._dev(h, experts, weights, w_gate, w_up, w_down, out)
         T, W = h.shape
         E, F = w_gate.shape[0], w_gate.shape[1]
@@ -1183,18 +1186,21 @@ class Ops:
             raise KernelError("moe_experts: float32 [tokens, width] output expected")
         entries = T * top
         most = cap * top
-        max_tiles = self.moe_max_tiles(entries, E)
-        plan = workspace.buffer("moe.plan" + tag, (E + 1 + most + 1 + 2 * self.moe_max_tiles(most, E),), torch.int32)
+        tc = 1 if (self.use_tensor_cores and h.dtype == torch.bfloat16 and W % 8 == 0 and F % 8 == 0 and _rows(h, "expert input") % 8 == 0
+                   and h.data_ptr() % 16 == 0) else 0
+        tile_rows = int(self.lib.hb_moe_tile_rows(tc))
+        max_tiles = self.moe_max_tiles(entries, E, tile_rows)
+        plan = workspace.buffer("moe.plan" + tag, (E + 1 + most + 1 + 2 * self.moe_max_tiles(most, E, 32),), torch.int32)
         offsets, order, tiles = plan[: E + 1], plan[E + 1: E + 1 + most], plan[E + 1 + most:]
         act = workspace.buffer("moe.act" + tag, (most, F), h.dtype)
         down = workspace.buffer("moe.down" + tag, (most, W), torch.float32)
         s = self._stream()
-        self._call("hb_moe_plan", experts.data_ptr(), entries, E, offsets.data_ptr(), order.data_ptr(), tiles.data_ptr(), s)
+        self._call("hb_moe_plan", experts.data_ptr(), entries, E, tile_rows, offsets.data_ptr(), order.data_ptr(), tiles.data_ptr(), s)
         self._call("hb_moe_glu", h.data_ptr(), _code(h), _rows(h, "expert input"), w_gate.data_ptr(), w_up.data_ptr(), _code(w_gate),
                    offsets.data_ptr(), order.data_ptr(), tiles.data_ptr(), max_tiles, top, act.data_ptr(), _code(act), F, F, W,
-                   float(limit), float(alpha), s)
+                   float(limit), float(alpha), tc, s)
         self._call("hb_moe_down", act.data_ptr(), _code(act), F, w_down.data_ptr(), _code(w_down), offsets.data_ptr(), order.data_ptr(),
-                   tiles.data_ptr(), max_tiles, top, down.data_ptr(), W, W, F, s)
+                   tiles.data_ptr(), max_tiles, top, down.data_ptr(), W, W, F, tc, s)
         self._call("hb_moe_combine", down.data_ptr(), W, weights.data_ptr(), top, out.data_ptr(), _rows(out, "expert output"), T, W,
                    1 if accumulate else 0, s)
         self.launches += 4
