@@ -159,6 +159,48 @@ extern "C" int hb_pool_blocks(const void* k_cache, const void* v_cache, int cach
 // Shared memory (floats): queries [AP_TQ][d], keys [AP_TK][d + 1], values [AP_TK][dv], weights [AP_TQ][AP_TK].
 static size_t ap_smem_bytes(int d, int dv) { return sizeof(float) * ((size_t)AP_TQ * d + (size_t)AP_TK * (d + 1) + (size_t)AP_TK * dv + AP_TQ * AP_TK); }
 
+// Stages up to AP_TK rows of `width` values (row kk at cache row k0 + kk of its page, kv head g) into shared memory as 32-bit
+// values, row stride ld_dst; rows beyond nk or without a page become zeros.  With rows of whole 16-byte chunks every thread
+// has four chunk loads in flight at a time; other widths go element by element.
+template <typename T>
+__device__ __forceinline__ void ap_stage(const T* __restrict__ cache, const int* pages, int nk, int k0, int g, int G, int width,
+                                         float* dst, int ld_dst, int tid) {
+    constexpr int EPC = 16 / (int)sizeof(T);
+    if (width % EPC == 0) {
+        const int cpr = width / EPC, total = AP_TK * cpr;
+        for (int base = 0; base < total; base += AP_THREADS * 4) {
+            uint4 raw[4];
+            int at[4];
+#pragma unroll
+            for (int u = 0; u < 4; u++) {
+                const int i = base + u * AP_THREADS + tid;
+                raw[u] = make_uint4(0u, 0u, 0u, 0u);
+                at[u] = -1;
+                if (i < total) {
+                    const int kk = i / cpr, ch = i - kk * cpr;
+                    at[u] = kk * ld_dst + ch * EPC;
+                    if (kk < nk && pages[kk] >= 0)
+                        raw[u] = *reinterpret_cast<const uint4*>(cache + cache_offset(pages[kk], g, k0 + kk, G, width) + ch * EPC);
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < 4; u++) {
+                if (at[u] < 0) continue;
+                const T* v = reinterpret_cast<const T*>(&raw[u]);
+#pragma unroll
+                for (int e = 0; e < EPC; e++) dst[at[u] + e] = to_f32(v[e]);
+            }
+        }
+        return;
+    }
+    for (int i = tid; i < AP_TK * width; i += AP_THREADS) {
+        const int kk = i / width, c = i - kk * width;
+        float v = 0.0f;
+        if (kk < nk && pages[kk] >= 0) v = to_f32(cache[cache_offset(pages[kk], g, k0 + kk, G, width) + c]);
+        dst[kk * ld_dst + c] = v;
+    }
+}
+
 template <typename TQ, typename TC, typename TO>
 __global__ void __launch_bounds__(AP_THREADS)
 attention_pool_kernel(const TQ* __restrict__ q, long long ldq, const TC* __restrict__ k_cache, const TC* __restrict__ v_cache,
@@ -237,23 +279,12 @@ attention_pool_kernel(const TQ* __restrict__ q, long long ldq, const TC* __restr
             pages[tid] = page;
         }
         __syncthreads();
-        for (int i = tid; i < AP_TK * d; i += AP_THREADS) {
-            const int kk = i / d, c = i - kk * d;
-            float v = 0.0f;
-            if (kk < nk && pages[kk] >= 0) {
-                const size_t off = cache_offset(pages[kk], g, k0 + kk, G, d) + c;
-                v = pooled ? pk_cache[off] : to_f32(k_cache[off]);
-            }
-            Ks[kk * (d + 1) + c] = v;
-        }
-        for (int i = tid; i < AP_TK * dv; i += AP_THREADS) {
-            const int kk = i / dv, c = i - kk * dv;
-            float v = 0.0f;
-            if (kk < nk && pages[kk] >= 0) {
-                const size_t off = cache_offset(pages[kk], g, k0 + kk, G, dv) + c;
-                v = pooled ? pv_cache[off] : to_f32(v_cache[off]);
-            }
-            Vs[kk * dv + c] = v;
+        if (pooled) {
+            ap_stage<float>(pk_cache, pages, nk, k0, g, G, d, Ks, d + 1, tid);
+            ap_stage<float>(pv_cache, pages, nk, k0, g, G, dv, Vs, dv, tid);
+        } else {
+            ap_stage<TC>(k_cache, pages, nk, k0, g, G, d, Ks, d + 1, tid);
+            ap_stage<TC>(v_cache, pages, nk, k0, g, G, dv, Vs, dv, tid);
         }
         __syncthreads();
         // weights: key `lane`, queries qg, qg + 4, qg + 8, qg + 12

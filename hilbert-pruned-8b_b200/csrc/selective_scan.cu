@@ -6,10 +6,10 @@
 // column range of a wider 32-bit matrix (row stride ldx).
 //
 // selective_scan: per token t, channel c, state index n (all 32-bit):
-//   dt_c = softplus(sum_r Wdt[c][r] low[t][r] + bdt[c]),  A[c][n] = -exp(A_log[c][n])
+//   dt_c = softplus(dt_raw[t][c] + bdt[c]),  A[c][n] = -exp(A_log[c][n])        (dt_raw: the step-size projection's result)
 //   S[c][n] <- exp(dt_c A[c][n]) S[c][n] + dt_c u[t][c] B[t][n]      (evaluated as S + expm1(dt A) S + dt u B)
 //   y[t][c] = sum_n S[c][n] C[t][n] + D[c] u[t][c];   out[t][c] = y silu(z[t][c])
-// with [low | B | C] the rows of one 32-bit matrix (the result of the projection of u).  A group
+// with [B | C] the rows of one 32-bit matrix (columns of the result of the projection of u).  A group
 // of SS_LANES threads owns a channel (state index n = lane, lane + SS_LANES, ...); a block owns
 // SS_CH channels of one sequence and walks its tokens in order, SS_TOK tokens of inputs staged
 // in shared memory at a time.  The state is read once and written once per step.
@@ -99,22 +99,23 @@ __device__ __forceinline__ float ss_softplus(float z) { return z > 20.0f ? z : l
 
 template <typename TU, typename TO, int LANES>
 __global__ void __launch_bounds__(SS_THREADS)
-selective_scan_kernel(const TU* __restrict__ u, long long ldu, const float* __restrict__ dbc, long long ldd,
-                      const float* __restrict__ z, long long ldz, const float* __restrict__ w_dt, const float* __restrict__ b_dt,
-                      const float* __restrict__ a_log, const float* __restrict__ dvec, float* __restrict__ state,
-                      long long state_stride, const int* __restrict__ state_slots, const int* __restrict__ seq_start,
-                      TO* __restrict__ out, long long ldo, int I, int N, int R) {
+selective_scan_kernel(const TU* __restrict__ u, long long ldu, const float* __restrict__ bc, long long ldb,
+                      const float* __restrict__ z, long long ldz, const float* __restrict__ dt_raw, long long lddt,
+                      const float* __restrict__ b_dt, const float* __restrict__ a_log, const float* __restrict__ dvec,
+                      float* __restrict__ state, long long state_stride, const int* __restrict__ state_slots,
+                      const int* __restrict__ seq_start, TO* __restrict__ out, long long ldo, int I, int N) {
     pdl_trigger();
     constexpr int CH = SS_THREADS / LANES;             // channels per block
     extern __shared__ float ss_smem[];
-    float* rows = ss_smem;                             // [SS_TOK][R + 2 N]: low | B | C of the staged tokens
-    float* us = rows + SS_TOK * (R + 2 * N);           // [SS_TOK][CH]
+    float* rows = ss_smem;                             // [SS_TOK][2 N]: B | C of the staged tokens
+    float* us = rows + SS_TOK * 2 * N;                 // [SS_TOK][CH]
     float* zs = us + SS_TOK * CH;                      // [SS_TOK][CH]
+    float* ds = zs + SS_TOK * CH;                      // [SS_TOK][CH]: the step sizes before bias and softplus
     const int tid = threadIdx.x, lane = tid % LANES, ch = tid / LANES;
     const int c = blockIdx.x * CH + ch, b = blockIdx.y;
     const bool live = c < I;
     const int start = seq_start[b], n_all = seq_start[b + 1] - start;
-    const int wrow = R + 2 * N;
+    const int wrow = 2 * N;
     float A[SS_MAX_PER], S[SS_MAX_PER];
 #pragma unroll
     for (int k = 0; k < SS_MAX_PER; k++) {
@@ -122,11 +123,11 @@ selective_scan_kernel(const TU* __restrict__ u, long long ldu, const float* __re
         A[k] = (live && n < N) ? -expf(a_log[(size_t)c * N + n]) : 0.0f;
     }
     const float bdt = live ? b_dt[c] : 0.0f, D = live ? dvec[c] : 0.0f;
-    const float* wd = w_dt + (size_t)(live ? c : 0) * R;
     pdl_wait();
     u = pdl_fresh(u);
-    dbc = pdl_fresh(dbc);
+    bc = pdl_fresh(bc);
     z = pdl_fresh(z);
+    dt_raw = pdl_fresh(dt_raw);
     state = pdl_fresh(state);
     float* srow = state + (size_t)state_slots[b] * state_stride + (size_t)(live ? c : 0) * N;
 #pragma unroll
@@ -139,21 +140,19 @@ selective_scan_kernel(const TU* __restrict__ u, long long ldu, const float* __re
         __syncthreads();
         for (int i = tid; i < nt * wrow; i += SS_THREADS) {
             const int j = i / wrow, r = i - j * wrow;
-            rows[j * wrow + r] = dbc[(size_t)(start + base + j) * ldd + r];
+            rows[j * wrow + r] = bc[(size_t)(start + base + j) * ldb + r];
         }
         for (int i = tid; i < nt * CH; i += SS_THREADS) {
             const int j = i / CH, k = i - j * CH, cc = blockIdx.x * CH + k;
-            us[i] = cc < I ? to_f32(u[(size_t)(start + base + j) * ldu + cc]) : 0.0f;
-            zs[i] = cc < I ? z[(size_t)(start + base + j) * ldz + cc] : 0.0f;
+            const size_t t = (size_t)(start + base + j);
+            us[i] = cc < I ? to_f32(u[t * ldu + cc]) : 0.0f;
+            zs[i] = cc < I ? z[t * ldz + cc] : 0.0f;
+            ds[i] = cc < I ? dt_raw[t * lddt + cc] : 0.0f;
         }
         __syncthreads();
         for (int j = 0; j < nt; j++) {
             const float* row = rows + j * wrow;
-            float part = 0.0f;
-            for (int r = lane; r < R; r += LANES) part = fmaf(wd[r], row[r], part);
-#pragma unroll
-            for (int o = LANES / 2; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o, LANES);
-            const float dt = ss_softplus(part + bdt);
+            const float dt = ss_softplus(ds[j * CH + ch] + bdt);
             const float uv = us[j * CH + ch];
             const float dtu = dt * uv;
             float y = 0.0f;
@@ -163,8 +162,8 @@ selective_scan_kernel(const TU* __restrict__ u, long long ldu, const float* __re
                 if (n < N) {
                     // S <- S + (exp(dt A) - 1) S + dt u B: with decays close to one, exp() rounded to 32 bits is off by up to
                     // 6e-8 of 1, i.e. by percents of the distance to one, and that error would grow with every token
-                    S[k] = fmaf(expm1f(dt * A[k]), S[k], fmaf(dtu, row[R + n], S[k]));
-                    y = fmaf(S[k], row[R + N + n], y);
+                    S[k] = fmaf(expm1f(dt * A[k]), S[k], fmaf(dtu, row[n], S[k]));
+                    y = fmaf(S[k], row[N + n], y);
                 }
             }
 #pragma unroll
@@ -186,33 +185,23 @@ selective_scan_kernel(const TU* __restrict__ u, long long ldu, const float* __re
 
 static int ss_lanes(int N) { return N <= 4 ? 4 : N <= 8 ? 8 : N <= 16 ? 16 : 32; }
 
-extern "C" int hb_selective_scan(const void* u, int u_dtype, long long ldu, const float* dbc, long long ldd, const float* z, long long ldz,
-                                 const float* w_dt, const float* b_dt, const float* a_log, const float* dvec, float* state,
+extern "C" int hb_selective_scan(const void* u, int u_dtype, long long ldu, const float* bc, long long ldb, const float* z, long long ldz,
+                                 const float* dt_raw, long long lddt, const float* b_dt, const float* a_log, const float* dvec, float* state,
                                  long long state_stride, const int* state_slots, const int* seq_start, void* out, int out_dtype,
-                                 long long ldo, int n_seqs, int inner, int n_state, int dt_rank, void* stream) {
+                                 long long ldo, int n_seqs, int inner, int n_state, void* stream) {
     if (n_seqs == 0) return 0;
-    HB_REQUIRE(n_seqs > 0 && n_seqs <= 65535 && inner > 0 && n_state > 0 && dt_rank > 0, "selective_scan: bad sizes");
+    HB_REQUIRE(n_seqs > 0 && n_seqs <= 65535 && inner > 0 && n_state > 0, "selective_scan: bad sizes");
     HB_REQUIRE(n_state <= SS_MAX_PER * 32, "selective_scan: state size %d (up to %d is built)", n_state, SS_MAX_PER * 32);
-    HB_REQUIRE(ldd >= dt_rank + 2 * n_state && ldu >= inner && ldz >= inner && ldo >= inner && state_stride >= (long long)inner * n_state,
+    HB_REQUIRE(ldb >= 2 * n_state && ldu >= inner && ldz >= inner && lddt >= inner && ldo >= inner && state_stride >= (long long)inner * n_state,
                "selective_scan: rows are too short");
     HB_REQUIRE(u_dtype == out_dtype && (u_dtype == HB_BF16 || u_dtype == HB_F32), "selective_scan: unsupported dtypes %d -> %d", u_dtype, out_dtype);
     const int lanes = ss_lanes(n_state), ch = SS_THREADS / lanes;
-    const size_t smem = sizeof(float) * ((size_t)SS_TOK * (dt_rank + 2 * n_state) + 2 * SS_TOK * ch);
-    HB_REQUIRE(smem <= 200 * 1024, "selective_scan: dt_rank + 2 * state = %d is too wide for the staging buffer", dt_rank + 2 * n_state);
+    const size_t smem = sizeof(float) * ((size_t)SS_TOK * 2 * n_state + 3 * SS_TOK * ch);
     dim3 grid((inner + ch - 1) / ch, n_seqs);
     cudaStream_t s = (cudaStream_t)stream;
 #define HB_SS(TU, TO, L)                                                                                                                  \
-    do {                                                                                                                                  \
-        static bool done[HB_MAX_DEVICES] = {};                                                                                            \
-        const int slot = hb_device_slot();                                                                                                \
-        if (!done[slot]) {                                                                                                                \
-            cudaError_t e = cudaFuncSetAttribute(selective_scan_kernel<TU, TO, L>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024); \
-            if (e != cudaSuccess) return hb_fail("selective_scan: shared memory: %s", cudaGetErrorString(e));                             \
-            done[slot] = true;                                                                                                            \
-        }                                                                                                                                 \
-        hb_launch(selective_scan_kernel<TU, TO, L>, dim3(grid), dim3(SS_THREADS), smem, s, (const TU*)u, ldu, dbc, ldd, z, ldz, w_dt, b_dt, \
-                  a_log, dvec, state, state_stride, state_slots, seq_start, (TO*)out, ldo, inner, n_state, dt_rank);                       \
-    } while (0)
+    hb_launch(selective_scan_kernel<TU, TO, L>, dim3(grid), dim3(SS_THREADS), smem, s, (const TU*)u, ldu, bc, ldb, z, ldz, dt_raw, lddt,  \
+              b_dt, a_log, dvec, state, state_stride, state_slots, seq_start, (TO*)out, ldo, inner, n_state)
 #define HB_SS_L(TU, TO)                                                                          \
     switch (lanes) {                                                                             \
         case 4: HB_SS(TU, TO, 4); break;                                                         \

@@ -90,8 +90,8 @@ _SIGNATURES = {
     "hb_gated_norm": [_c_ptr, _c_ll, _c_ptr, _c_ll, _c_ptr, _c_float, _c_float, _c_ptr, _c_int, _c_ll, _c_int, _c_int, _c_ptr],
     "hb_conv_act": [_c_ptr, _c_ll, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_ll, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_ll, _c_int, _c_int, _c_int,
                     _c_int, _c_ptr],
-    "hb_selective_scan": [_c_ptr, _c_int, _c_ll, _c_ptr, _c_ll, _c_ptr, _c_ll, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ll, _c_ptr, _c_ptr,
-                          _c_ptr, _c_int, _c_ll, _c_int, _c_int, _c_int, _c_int, _c_ptr],
+    "hb_selective_scan": [_c_ptr, _c_int, _c_ll, _c_ptr, _c_ll, _c_ptr, _c_ll, _c_ptr, _c_ll, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ll, _c_ptr,
+                          _c_ptr, _c_ptr, _c_int, _c_ll, _c_int, _c_int, _c_int, _c_ptr],
     "hb_moe_route": [_c_ptr, _c_int, _c_ll, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_ptr],
     "hb_moe_plan": [_c_ptr, _c_int, _c_int, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_ptr],
     "hb_moe_glu": [_c_ptr, _c_int, _c_ll, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_ptr, _c_int, _c_ll, _c_int,
@@ -1042,13 +1042,13 @@ class Ops:
     ATTENTION_POOL_MAX_SPLITS = 64
 
     def attention_pool_splits(self, step, heads: int, window: Optional[int], pool: int) -> int:
-        """Key ranges a step is cut into: one unless the step's blocks would leave most of the device idle and a
-        query sees enough keys (decode steps over long sequences)."""
+        """Key ranges a step is cut into: one unless the step's blocks are fewer than two per SM and a query sees
+        enough keys (decode steps), then as many as give every SM two blocks, of 64 keys or more each."""
         tiles = sum(-(-n // self.ATTENTION_POOL_TILE) for n in step.host_new) * heads
         keys = step.max_len if not window else min(step.max_len, window + step.max_new) + (step.max_len // pool if pool else 0)
-        if tiles >= self.sm_count or keys < 256:
+        if tiles >= 2 * self.sm_count or keys < 256:
             return 1
-        return max(1, min(self.ATTENTION_POOL_MAX_SPLITS, self.sm_count // tiles, keys // 128))
+        return max(1, min(self.ATTENTION_POOL_MAX_SPLITS, -(-2 * self.sm_count // tiles), keys // 64))
 
     def attention_pool(self, q, cache, pooled, step, head_bias, gate, out, heads: int, kv_heads: int, head_dim: int, v_dim: int,
                        scale: float, window: Optional[int], pool: int, workspace=None) -> None:
@@ -1130,24 +1130,24 @@ class Ops:
                    _rows(out, "conv_act output"), step.num_seqs, step.max_new, C, self.ACTIVATIONS[activation], self._stream())
         self.launches += 1
 
-    def selective_scan(self, u, dbc, z, w_dt, b_dt, a_log, d_skip, state, step, out, dt_rank: int, n_state: int) -> None:
-        """The selective scan over a step's tokens, sequence by sequence: ``dbc`` float32 rows ``[dt low rank | B | C]``, ``z``
-        float32 gate input, ``u`` and ``out`` in the activations' dtype ``[tokens, inner]``; ``state`` float32 ``[slots, inner * n_state]``."""
-        self._dev(u, dbc, z, w_dt, b_dt, a_log, d_skip, state, out)
+    def selective_scan(self, u, bc, z, dt_raw, b_dt, a_log, d_skip, state, step, out, n_state: int) -> None:
+        """The selective scan over a step's tokens, sequence by sequence: ``bc`` float32 rows ``[B | C]``, ``z`` float32 gate
+        input, ``dt_raw`` float32 ``[tokens, inner]`` (the step sizes before bias and softplus), ``u`` and ``out`` in the
+        activations' dtype ``[tokens, inner]``; ``state`` float32 ``[slots, inner * n_state]``."""
+        self._dev(u, bc, z, dt_raw, b_dt, a_log, d_skip, state, out)
         T, inner = u.shape
-        if dbc.dtype != torch.float32 or z.dtype != torch.float32 or tuple(z.shape) != (T, inner) or tuple(out.shape) != (T, inner) \
-                or dbc.shape[0] != T or dbc.shape[1] < dt_rank + 2 * n_state or u.dtype != out.dtype:
+        if any(t.dtype != torch.float32 for t in (bc, z, dt_raw)) or tuple(z.shape) != (T, inner) or tuple(dt_raw.shape) != (T, inner) \
+                or tuple(out.shape) != (T, inner) or tuple(bc.shape) != (T, 2 * n_state) or u.dtype != out.dtype:
             raise KernelError("selective_scan: shapes or dtypes do not agree")
-        if tuple(w_dt.shape) != (inner, dt_rank) or w_dt.dtype != torch.float32 or not w_dt.is_contiguous() \
-                or tuple(a_log.shape) != (inner, n_state) or a_log.dtype != torch.float32 or not a_log.is_contiguous():
-            raise KernelError("selective_scan: float32 step-size weights [inner, dt_rank] and A_log [inner, state] expected")
+        if tuple(a_log.shape) != (inner, n_state) or a_log.dtype != torch.float32 or not a_log.is_contiguous():
+            raise KernelError("selective_scan: float32 A_log [inner, state] expected")
         if state.dtype != torch.float32 or state.dim() != 2 or state.shape[1] != inner * n_state or state.stride(1) != 1:
             raise KernelError("selective_scan: state must be float32 [slots, inner * state]")
-        self._call("hb_selective_scan", u.data_ptr(), _code(u), _rows(u, "scan input"), dbc.data_ptr(), _rows(dbc, "scan parameters"),
-                   z.data_ptr(), _rows(z, "scan gate"), w_dt.data_ptr(), self._f32_vec(b_dt, inner, "step-size bias"), a_log.data_ptr(),
-                   self._f32_vec(d_skip, inner, "skip weight"), state.data_ptr(), state.stride(0), step.state_slots.data_ptr(),
-                   step.seq_start.data_ptr(), out.data_ptr(), _code(out), _rows(out, "scan output"), step.num_seqs, inner, n_state,
-                   dt_rank, self._stream())
+        self._call("hb_selective_scan", u.data_ptr(), _code(u), _rows(u, "scan input"), bc.data_ptr(), _rows(bc, "scan parameters"),
+                   z.data_ptr(), _rows(z, "scan gate"), dt_raw.data_ptr(), _rows(dt_raw, "step sizes"),
+                   self._f32_vec(b_dt, inner, "step-size bias"), a_log.data_ptr(), self._f32_vec(d_skip, inner, "skip weight"),
+                   state.data_ptr(), state.stride(0), step.state_slots.data_ptr(), step.seq_start.data_ptr(), out.data_ptr(), _code(out),
+                   _rows(out, "scan output"), step.num_seqs, inner, n_state, self._stream())
         self.launches += 1
 
     # ------------------------------------------------------------------ mixture of experts

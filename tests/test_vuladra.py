@@ -385,9 +385,10 @@ def test_convolution_and_selective_scan_carry_their_state_over_portions(inner, n
         T = pin.shape[0]
         u = torch.empty(T, I, device="cuda")
         ops.conv_act(pin[:, :I], cw.cuda(), cb.cuda(), state[:, :conv_state], step, u, "silu")
-        dbc = (u.double() @ wx.double().cuda().T).float().contiguous()       # the projection itself is not under test here
+        dbc = (u.double() @ wx.double().cuda().T).float().contiguous()       # the projections themselves are not under test here
+        dt_raw = (dbc[:, :R].double() @ wdt.double().cuda().T).float().contiguous()
         y = torch.empty(T, I, device="cuda")
-        ops.selective_scan(u, dbc, pin[:, I:2 * I], wdt.cuda(), bdt.cuda(), a_log.cuda(), D.cuda(), state[:, conv_state:], step, y, R, N)
+        ops.selective_scan(u, dbc[:, R:], pin[:, I:2 * I], dt_raw, bdt.cuda(), a_log.cuda(), D.cuda(), state[:, conv_state:], step, y, N)
         uc, yc, at = u.cpu(), y.cpu(), 0
         for i, n in zip(live, new):
             got_u[i].append(uc[at: at + n])
