@@ -176,7 +176,14 @@ int hb_attention_pool(const void* q, int q_dtype, long long ldq, const void* k_c
                       const int* seq_start, const int* seq_pos0, int n_seqs, int q_tiles, const float* head_bias, const float* gate,
                       long long ldg, void* out, int out_dtype, long long ldo, float* partial, int n_tokens, int n_heads, int n_kv_heads,
                       int head_dim, int v_dim, float scale, int window, int pool, int n_pages_tok, int n_pages_pool, int splits,
-                      int* status, void* stream);
+                      int part, int* status, void* stream);       // part 1: the pooled blocks alone, unweighted by the gate, into partial
+// the window part on the tensor cores (attention_pool_prefill.cu): bfloat16, head sizes 64 or 128, q_blocks = sum of ceil(new / 64);
+// pooled: what hb_attention_pool made with part 1 (float32 [tokens][heads * v_dim]) or null
+int hb_attention_pool_prefill_supported(int head_dim, int v_dim);
+int hb_attention_pool_prefill(const void* q, long long q_stride, const void* k_cache, const void* v_cache, const int* page_table,
+                              int pt_width, const int* seq_start, const int* seq_pos0, const float* head_bias, const float* pooled,
+                              const float* gate, long long ldg, void* out, long long out_stride, int n_seqs, int q_blocks, int n_heads,
+                              int n_kv_heads, int head_dim, int v_dim, float scale, int window, int n_pages, int* status, void* stream);
 // Matrix memory with a fixed decay per head (decay_memory.cu).  proj rows: [q heads*d | k heads*d | v heads*dv | ...] float32;
 // state per slot: S [heads][d][dv]; out [tokens][heads*dv] float32; act 1: silu on q, k and v
 int hb_decay_memory(const float* proj, long long ldp, const float* decay, float* state, long long state_stride, const int* state_slots,

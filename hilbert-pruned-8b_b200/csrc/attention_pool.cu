@@ -209,7 +209,7 @@ attention_pool_kernel(const TQ* __restrict__ q, long long ldq, const TC* __restr
                       const int* __restrict__ seq_pos0, int n_seqs, const float* __restrict__ head_bias,
                       const float* __restrict__ gate, long long ldg, TO* __restrict__ out, long long ldo, float* __restrict__ partial,
                       int n_tokens, int H, int G, int d, int dv, float scale, int window, int P, int n_pages_tok, int n_pages_pool,
-                      int splits, int* status) {
+                      int splits, int part, int* status) {
     pdl_trigger();
     extern __shared__ float ap_smem[];
     float* Qs = ap_smem;
@@ -246,7 +246,7 @@ attention_pool_kernel(const TQ* __restrict__ q, long long ldq, const TC* __restr
     const int nb = (P > 0 && window > 0 && p_last - window + 1 >= P) ? (p_last - window + 1) / P : 0;
     const int j_lo = window > 0 ? max(0, p_first - window + 1) : 0;
     const int pool_tiles = (nb + AP_TK - 1) / AP_TK;
-    const int tok_tiles = (p_last - j_lo + 1 + AP_TK - 1) / AP_TK;
+    const int tok_tiles = part == 1 ? 0 : (p_last - j_lo + 1 + AP_TK - 1) / AP_TK;      // part 1: the pooled blocks alone
     const int all_tiles = pool_tiles + tok_tiles;
     const int per_split = (all_tiles + splits - 1) / splits;
     const int tile_lo = split * per_split, tile_hi = min(all_tiles, tile_lo + per_split);
@@ -333,7 +333,7 @@ attention_pool_kernel(const TQ* __restrict__ q, long long ldq, const TC* __restr
             const int c = lane + 32 * m;
             if (c >= dv) continue;
             const size_t col = (size_t)h * dv + c;
-            if (splits == 1) {
+            if (splits == 1 && part == 0) {
                 float v = acc[a][m];
                 if (gate != nullptr) v *= 1.0f / (1.0f + expf(-gate[(size_t)t * ldg + col]));
                 out[(size_t)t * ldo + col] = from_f32<TO>(v);
@@ -370,13 +370,14 @@ extern "C" int hb_attention_pool(const void* q, int q_dtype, long long ldq, cons
                                  const int* seq_start, const int* seq_pos0, int n_seqs, int q_tiles, const float* head_bias,
                                  const float* gate, long long ldg, void* out, int out_dtype, long long ldo, float* partial,
                                  int n_tokens, int n_heads, int n_kv_heads, int head_dim, int v_dim, float scale, int window,
-                                 int pool, int n_pages_tok, int n_pages_pool, int splits, int* status, void* stream) {
+                                 int pool, int n_pages_tok, int n_pages_pool, int splits, int part, int* status, void* stream) {
     if (n_tokens == 0) return 0;
     HB_REQUIRE(n_tokens > 0 && n_seqs > 0 && q_tiles > 0 && n_heads > 0 && n_kv_heads > 0 && n_heads % n_kv_heads == 0, "attention_pool: bad sizes");
     HB_REQUIRE(hb_attention_pool_supported(head_dim, v_dim), "attention_pool: head sizes %d / %d (up to %d are built)", head_dim, v_dim, AP_MAX_DIM);
     HB_REQUIRE(n_heads <= 65535 && splits >= 1 && splits <= 65535, "attention_pool: too many heads or key ranges");
     HB_REQUIRE(pool == 0 || (pk_cache != nullptr && pv_cache != nullptr && pt_pool != nullptr && window > 0), "attention_pool: pooled blocks need their store and a window");
-    HB_REQUIRE(splits == 1 || partial != nullptr, "attention_pool: key ranges need a buffer for their sums");
+    HB_REQUIRE((splits == 1 && part == 0) || partial != nullptr, "attention_pool: key ranges need a buffer for their sums");
+    HB_REQUIRE(part == 0 || (part == 1 && splits == 1 && pool > 0), "attention_pool: the pooled blocks alone are one range");
     cudaStream_t s = (cudaStream_t)stream;
     const size_t smem = ap_smem_bytes(head_dim, v_dim);
     dim3 grid(q_tiles, n_heads, splits);
@@ -393,7 +394,7 @@ extern "C" int hb_attention_pool(const void* q, int q_dtype, long long ldq, cons
         hb_launch(attention_pool_kernel<TQ, TC, TO>, dim3(grid), dim3(AP_THREADS), smem, s, (const TQ*)q, ldq, (const TC*)k_cache,         \
                   (const TC*)v_cache, pk_cache, pv_cache, pt_tok, pt_pool, pt_width, seq_start, seq_pos0, n_seqs, head_bias, gate, ldg,    \
                   (TO*)out, ldo, partial, n_tokens, n_heads, n_kv_heads, head_dim, v_dim, scale, window, pool, n_pages_tok, n_pages_pool,  \
-                  splits, status);                                                                                                         \
+                  splits, part, status);                                                                                                   \
     } while (0)
     if (q_dtype == HB_BF16 && cache_dtype == HB_BF16 && out_dtype == HB_BF16) HB_AP(bf16, bf16, bf16);
     else if (q_dtype == HB_F32 && cache_dtype == HB_F32 && out_dtype == HB_F32) HB_AP(float, float, float);

@@ -92,7 +92,7 @@ extern "C" int hb_conv_act(const float* x, long long ldx, const float* conv_w, c
 
 // ------------------------------------------------------------------------------------------------ selective_scan
 #define SS_THREADS 256
-#define SS_TOK 16           // tokens of inputs staged at a time
+#define SS_TOK 32           // tokens of inputs staged at a time
 #define SS_MAX_PER 8        // state values a thread holds: state sizes up to SS_MAX_PER * lanes
 
 __device__ __forceinline__ float ss_softplus(float z) { return z > 20.0f ? z : log1pf(expf(z)); }
@@ -109,8 +109,8 @@ selective_scan_kernel(const TU* __restrict__ u, long long ldu, const float* __re
     extern __shared__ float ss_smem[];
     float* rows = ss_smem;                             // [SS_TOK][2 N]: B | C of the staged tokens
     float* us = rows + SS_TOK * 2 * N;                 // [SS_TOK][CH]
-    float* zs = us + SS_TOK * CH;                      // [SS_TOK][CH]
-    float* ds = zs + SS_TOK * CH;                      // [SS_TOK][CH]: the step sizes before bias and softplus
+    float* zs = us + SS_TOK * CH;                      // [SS_TOK][CH]: silu(z)
+    float* ds = zs + SS_TOK * CH;                      // [SS_TOK][CH]: the step sizes
     const int tid = threadIdx.x, lane = tid % LANES, ch = tid / LANES;
     const int c = blockIdx.x * CH + ch, b = blockIdx.y;
     const bool live = c < I;
@@ -122,7 +122,7 @@ selective_scan_kernel(const TU* __restrict__ u, long long ldu, const float* __re
         const int n = lane + k * LANES;
         A[k] = (live && n < N) ? -expf(a_log[(size_t)c * N + n]) : 0.0f;
     }
-    const float bdt = live ? b_dt[c] : 0.0f, D = live ? dvec[c] : 0.0f;
+    const float D = live ? dvec[c] : 0.0f;
     pdl_wait();
     u = pdl_fresh(u);
     bc = pdl_fresh(bc);
@@ -145,14 +145,16 @@ selective_scan_kernel(const TU* __restrict__ u, long long ldu, const float* __re
         for (int i = tid; i < nt * CH; i += SS_THREADS) {
             const int j = i / CH, k = i - j * CH, cc = blockIdx.x * CH + k;
             const size_t t = (size_t)(start + base + j);
+            // what depends on (token, channel) alone is made here, once and by all threads, not in the walk below
             us[i] = cc < I ? to_f32(u[t * ldu + cc]) : 0.0f;
-            zs[i] = cc < I ? z[t * ldz + cc] : 0.0f;
-            ds[i] = cc < I ? dt_raw[t * lddt + cc] : 0.0f;
+            const float zv = cc < I ? z[t * ldz + cc] : 0.0f;
+            zs[i] = zv / (1.0f + expf(-zv));
+            ds[i] = cc < I ? ss_softplus(dt_raw[t * lddt + cc] + b_dt[cc]) : 0.0f;
         }
         __syncthreads();
         for (int j = 0; j < nt; j++) {
             const float* row = rows + j * wrow;
-            const float dt = ss_softplus(ds[j * CH + ch] + bdt);
+            const float dt = ds[j * CH + ch];
             const float uv = us[j * CH + ch];
             const float dtu = dt * uv;
             float y = 0.0f;
@@ -169,8 +171,7 @@ selective_scan_kernel(const TU* __restrict__ u, long long ldu, const float* __re
 #pragma unroll
             for (int o = LANES / 2; o > 0; o >>= 1) y += __shfl_xor_sync(0xffffffffu, y, o, LANES);
             if (lane == 0 && live) {
-                const float zv = zs[j * CH + ch];
-                out[(size_t)(start + base + j) * ldo + c] = from_f32<TO>((y + D * uv) * (zv / (1.0f + expf(-zv))));
+                out[(size_t)(start + base + j) * ldo + c] = from_f32<TO>((y + D * uv) * zs[j * CH + ch]);
             }
         }
     }

@@ -85,7 +85,9 @@ _SIGNATURES = {
                        _c_int, _c_int, _c_int, _c_int, _c_ptr, _c_ptr],
     "hb_attention_pool": [_c_ptr, _c_int, _c_ll, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_int,
                           _c_int, _c_ptr, _c_ptr, _c_ll, _c_ptr, _c_int, _c_ll, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float,
-                          _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr, _c_ptr],
+                          _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr, _c_ptr],
+    "hb_attention_pool_prefill": [_c_ptr, _c_ll, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ll, _c_ptr, _c_ll,
+                                  _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_int, _c_ptr, _c_ptr],
     "hb_decay_memory": [_c_ptr, _c_ll, _c_ptr, _c_ptr, _c_ll, _c_ptr, _c_ptr, _c_ptr, _c_ll, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr],
     "hb_gated_norm": [_c_ptr, _c_ll, _c_ptr, _c_ll, _c_ptr, _c_float, _c_float, _c_ptr, _c_int, _c_ll, _c_int, _c_int, _c_ptr],
     "hb_conv_act": [_c_ptr, _c_ll, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_ll, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_ll, _c_int, _c_int, _c_int,
@@ -108,6 +110,12 @@ _lib = None
 
 class KernelError(RuntimeError):
     pass
+
+
+def workspace_rows(workspace, rows: int) -> int:
+    """Rows to ask a workspace for when a buffer's size follows a step's tokens: whole thousands, so that steps of similar
+    sizes share one allocation."""
+    return -(-int(rows) // 1024) * 1024
 
 
 def load_library():
@@ -135,6 +143,7 @@ def load_library():
         lib.hb_attention_heads_variant.argtypes, lib.hb_attention_heads_variant.restype = [_c_int] * 6, _c_int
         lib.hb_attention_heads_writes_output.argtypes, lib.hb_attention_heads_writes_output.restype = [_c_int] * 6, _c_int
         lib.hb_attention_pool_supported.argtypes, lib.hb_attention_pool_supported.restype = [_c_int] * 2, _c_int
+        lib.hb_attention_pool_prefill_supported.argtypes, lib.hb_attention_pool_prefill_supported.restype = [_c_int] * 2, _c_int
         lib.hb_moe_max_tiles.argtypes, lib.hb_moe_max_tiles.restype = [_c_int] * 3, _c_int
         lib.hb_moe_tile_rows.argtypes, lib.hb_moe_tile_rows.restype = [_c_int], _c_int
         lib.hb_attention_decode_ctas_per_sm.argtypes, lib.hb_attention_decode_ctas_per_sm.restype = [_c_int], _c_int
@@ -293,6 +302,7 @@ class Ops:
         # terms) where the sizes allow; tests switch it off to compare with the FP32-pipe variant
         self.use_mma_attention = True
         self.use_flash_sink_attention = True    # steps of many tokens: attention_sink_prefill where it is built
+        self.use_mma_pool_attention = True      # steps of many tokens: attention_pool_prefill where it is built (tests compare both)
         # Decode attention that rotates the new queries and key and appends to the cache itself
         # (no rotation kernel in front; the new key and value go into the owning split's copy of
         # their page in shared memory).  Inside a replayed graph at batch 8 / 8192 tokens it takes
@@ -1038,6 +1048,7 @@ class Ops:
                    self._stream())
         self.launches += 1
 
+    POOL_PREFILL_FROM = 16              # steps whose longest portion has at least so many tokens run the tensor-core kernel
     ATTENTION_POOL_TILE = 16            # query tokens of a sequence that share a block
     ATTENTION_POOL_MAX_SPLITS = 64
 
@@ -1067,20 +1078,41 @@ class Ops:
             raise KernelError("attention_pool: pooled blocks need their store and a window")
         pt = step.page_tables[cache.group]
         pp = step.page_tables[pooled.group] if pool else None
+        bias_ptr = self._f32_vec(head_bias, heads, "head bias") if head_bias is not None else None
+        common = (pooled.k.data_ptr() if pool else None, pooled.v.data_ptr() if pool else None, pt.data_ptr(),
+                  pp.data_ptr() if pool else None, pt.shape[1], step.seq_start.data_ptr(), step.seq_pos0.data_ptr(), step.num_seqs)
+        tiles = sum(-(-n // self.ATTENTION_POOL_TILE) for n in step.host_new)
+        sizes = (T, heads, kv_heads, head_dim, v_dim, float(scale), int(window) if window else 0, int(pool) if pool else 0,
+                 cache.k.shape[0], pooled.k.shape[0] if pool else 0)
+        if (self.use_mma_pool_attention and q.dtype == torch.bfloat16 and cache.k.dtype == torch.bfloat16 and out.dtype == torch.bfloat16
+                and not step.is_decode and step.max_new >= self.POOL_PREFILL_FROM
+                and self.lib.hb_attention_pool_prefill_supported(head_dim, v_dim) and _rows(q, "queries") % 2 == 0
+                and _rows(out, "attention output") % 2 == 0 and sum(-(-n // 64) for n in step.host_new) <= 65535):
+            # many tokens: the window on the tensor cores, 64 query tokens a block; the pooled blocks, few, by the FP32 kernel first
+            share = None
+            if pool:
+                share = workspace.buffer("attention_pool.pooled_share", (workspace_rows(workspace, T), heads * v_dim), torch.float32)[:T]
+                self._call("hb_attention_pool", q.data_ptr(), _code(q), _rows(q, "queries"), cache.k.data_ptr(), cache.v.data_ptr(),
+                           _code(cache.k), *common, tiles, bias_ptr, None, 0, out.data_ptr(), _code(out), _rows(out, "attention output"),
+                           share.data_ptr(), *sizes, 1, 1, self.status.data_ptr(), self._stream())
+                self.launches += 1
+            self._call("hb_attention_pool_prefill", q.data_ptr(), _rows(q, "queries"), cache.k.data_ptr(), cache.v.data_ptr(), pt.data_ptr(),
+                       pt.shape[1], step.seq_start.data_ptr(), step.seq_pos0.data_ptr(), bias_ptr,
+                       share.data_ptr() if share is not None else None, gate.data_ptr() if gate is not None else None,
+                       _rows(gate, "gate") if gate is not None else 0, out.data_ptr(), _rows(out, "attention output"), step.num_seqs,
+                       sum(-(-n // 64) for n in step.host_new), heads, kv_heads, head_dim, v_dim, float(scale), int(window) if window else 0,
+                       cache.k.shape[0], self.status.data_ptr(), self._stream())
+            self.launches += 1
+            return
         splits = self.attention_pool_splits(step, heads, window, pool)
         partial = None
         if splits > 1:
             # the same buffer for every step of a shape: a captured graph holds its address
             partial = workspace.buffer(f"attention_pool.partial{step.tag}.{splits}", (splits, T, heads * v_dim), torch.float32)
-        tiles = sum(-(-n // self.ATTENTION_POOL_TILE) for n in step.host_new)
         self._call("hb_attention_pool", q.data_ptr(), _code(q), _rows(q, "queries"), cache.k.data_ptr(), cache.v.data_ptr(),
-                   _code(cache.k), pooled.k.data_ptr() if pool else None, pooled.v.data_ptr() if pool else None, pt.data_ptr(),
-                   pp.data_ptr() if pool else None, pt.shape[1], step.seq_start.data_ptr(), step.seq_pos0.data_ptr(), step.num_seqs,
-                   tiles, self._f32_vec(head_bias, heads, "head bias") if head_bias is not None else None,
-                   gate.data_ptr() if gate is not None else None, _rows(gate, "gate") if gate is not None else 0, out.data_ptr(),
-                   _code(out), _rows(out, "attention output"), partial.data_ptr() if partial is not None else None, T, heads, kv_heads,
-                   head_dim, v_dim, float(scale), int(window) if window else 0, int(pool) if pool else 0, cache.k.shape[0],
-                   pooled.k.shape[0] if pool else 0, splits, self.status.data_ptr(), self._stream())
+                   _code(cache.k), *common, tiles, bias_ptr, gate.data_ptr() if gate is not None else None,
+                   _rows(gate, "gate") if gate is not None else 0, out.data_ptr(), _code(out), _rows(out, "attention output"),
+                   partial.data_ptr() if partial is not None else None, *sizes, splits, 0, self.status.data_ptr(), self._stream())
         self.launches += 1 if splits == 1 else 2
 
     # ------------------------------------------------------------------ matrix memory with a fixed decay

@@ -234,7 +234,8 @@ def test_norm_on_a_sublayer_output_and_the_weighted_sum():
 @pytest.mark.gpu
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("H,G,d,dv,size,P", [(4, 2, 16, 8, 20, 6), (1, 1, 8, 12, 1, 1), (3, 3, 4, 4, 1000, 7), (4, 2, 64, 32, 33, 48),
-                                             (2, 1, 32, 64, 100, 16), (6, 2, 24, 40, 64, 64), (2, 2, 128, 256, 37, 5), (2, 1, 16, 16, 50, 0)])
+                                             (2, 1, 32, 64, 100, 16), (6, 2, 24, 40, 64, 64), (2, 2, 128, 256, 37, 5), (2, 1, 16, 16, 50, 0),
+                                             (4, 2, 64, 64, 40, 16), (2, 1, 128, 128, 70, 48), (2, 2, 64, 128, 33, 5), (2, 1, 128, 64, 200, 0)])
 def test_pooled_window_attention_sees_exactly_the_window_and_the_whole_blocks(H, G, d, dv, size, P, dtype):
     """A prompt of 300 tokens, then tokens one by one.  For some queries one key is made to stand out (its score is far above
     the others, which are pushed far below zero by the heads' biases): the token just inside the window, the one just outside
@@ -540,6 +541,23 @@ def test_the_two_norms_between_sublayers_in_one_pass_or_two(models, name):
     b = tt.run_in_process(eng, steps)
     for k in a:
         assert (a[k] - b[k]).abs().max() < 1e-4
+
+
+@pytest.mark.gpu
+def test_prompt_attention_on_the_tensor_cores_equals_the_fp32_kernel(models):
+    """bfloat16 prompts with head sizes of 64: the window on the tensor cores plus the pooled blocks' share, against the
+    kernel that does both on the FP32 pipe."""
+    require_gpu()
+    folder, cfg, plain = models["wide"]
+    v = cfg["vocab"]
+    batches = [{f"k{i}": (tt.random_tokens(n, v, 950 + i), p) for i, (n, p) in enumerate([(260, 250), (20, 17), (70, 64)])}]
+    steps, peak = tt.trace_batches(batches)
+    a = tt.run_in_process(_engine(folder, "bfloat16", peak), steps)
+    eng = _engine(folder, "bfloat16", peak)
+    eng.ctx.ops.use_mma_pool_attention = False
+    b = tt.run_in_process(eng, steps)
+    close = sum((a[k] - b[k]).abs().max().item() <= 2e-2 * max(1.0, b[k].abs().max().item()) for k in a)
+    assert close >= 0.9 * len(a), f"{len(a) - close} of {len(a)} positions differ"      # (a router's near tie may fall the other way)
 
 
 def _greedy(plain, prompt, n):

@@ -64,11 +64,11 @@ EDGES = config(48, 130, [
     with_mlp(parallel((2, 2, 8, 4, 1000), (1, 4, 4, (1.0,)), 0.5, 1.5), moe(4, 1, 16, 1.0)),
     with_mlp(attention(3, 3, 4, 4, 1000, 7), dense(24)),
     with_mlp(parallel((3, 1, 8, 8, 1), (3, 8, 4, (0.0, 0.5, 0.9))), None)], eps=1e-6)
-# widths the tensor-core products take; head sizes of 64 and 128 (the flash-style prompt kernel of the softmax branch);
+# widths the tensor-core products take; head sizes of 64 and 128 (the tensor-core prompt kernels of both kinds of attention);
 # blocks that straddle page borders (48 does not divide 64), a window shorter than a block, state sizes above 32
 WIDE = config(128, 300, [
     with_mlp(mamba(256, 40, 16, 4), moe(8, 2, 64, 2.0, (64, 1.5))),
-    with_mlp(attention(4, 2, 64, 32, 33, 48), dense(192)),
+    with_mlp(attention(4, 2, 64, 64, 33, 48), dense(192)),
     with_mlp(parallel((2, 1, 64, 64, 70), (2, 32, 64, (0.9, 0.999))), moe(8, 3, 32, 1.0)),
     with_mlp(attention(2, 1, 32, 64, 100, 16), None),
     with_mlp(parallel((2, 2, 128, 64, 40), (4, 16, 16, (0.5, 0.8, 0.95, 0.99))), dense(64))])
