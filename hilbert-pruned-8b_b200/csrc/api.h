@@ -176,7 +176,8 @@ int hb_attention_pool(const void* q, int q_dtype, long long ldq, const void* k_c
                       const int* seq_start, const int* seq_pos0, int n_seqs, int q_tiles, const float* head_bias, const float* gate,
                       long long ldg, void* out, int out_dtype, long long ldo, float* partial, int n_tokens, int n_heads, int n_kv_heads,
                       int head_dim, int v_dim, float scale, int window, int pool, int n_pages_tok, int n_pages_pool, int splits,
-                      int part, int* status, void* stream);       // part 1: the pooled blocks alone, unweighted by the gate, into partial
+                      int part, int grouped, int* status, void* stream);   // part 1: the pooled blocks alone, without the gate, into partial;
+                                                                            // grouped: one token per sequence, a block's rows are a kv head's query heads
 // the window part on the tensor cores (attention_pool_prefill.cu): bfloat16, head sizes 64 or 128, q_blocks = sum of ceil(new / 64);
 // pooled: what hb_attention_pool made with part 1 (float32 [tokens][heads * v_dim]) or null
 int hb_attention_pool_prefill_supported(int head_dim, int v_dim);

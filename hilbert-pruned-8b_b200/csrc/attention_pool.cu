@@ -209,7 +209,7 @@ attention_pool_kernel(const TQ* __restrict__ q, long long ldq, const TC* __restr
                       const int* __restrict__ seq_pos0, int n_seqs, const float* __restrict__ head_bias,
                       const float* __restrict__ gate, long long ldg, TO* __restrict__ out, long long ldo, float* __restrict__ partial,
                       int n_tokens, int H, int G, int d, int dv, float scale, int window, int P, int n_pages_tok, int n_pages_pool,
-                      int splits, int part, int* status) {
+                      int splits, int part, int grouped, int* status) {
     pdl_trigger();
     extern __shared__ float ap_smem[];
     float* Qs = ap_smem;
@@ -217,8 +217,12 @@ attention_pool_kernel(const TQ* __restrict__ q, long long ldq, const TC* __restr
     float* Vs = Ks + AP_TK * (d + 1);
     float* Ps = Vs + AP_TK * dv;
     __shared__ int pages[AP_TK];
-    const int tid = threadIdx.x, h = blockIdx.y, split = blockIdx.z;
-    const int g = h / (H / G);
+    // grouped (steps of one token per sequence): a block serves the query heads of ONE key/value head as its rows, so the
+    // group's keys and values are staged once instead of once per head; else its rows are up to AP_TQ tokens of one head
+    const int R = H / G;
+    const int tid = threadIdx.x, split = blockIdx.z;
+    const int g = grouped ? (int)blockIdx.y : (int)blockIdx.y / R;
+    const int h0 = grouped ? g * R : (int)blockIdx.y;          // the head of row 0
     // which sequence and which of its query tiles (the step's metadata was copied before the step's first kernel)
     int b = 0, tile = blockIdx.x;
     for (; b < n_seqs; b++) {
@@ -228,9 +232,8 @@ attention_pool_kernel(const TQ* __restrict__ q, long long ldq, const TC* __restr
     }
     if (b >= n_seqs) return;
     const int t0 = seq_start[b] + tile * AP_TQ;
-    const int nq = min(AP_TQ, seq_start[b + 1] - t0);
-    const int p_first = seq_pos0[b] + tile * AP_TQ, p_last = p_first + nq - 1;
-    const float bias = head_bias != nullptr ? head_bias[h] : 0.0f;
+    const int nq = grouped ? R : min(AP_TQ, seq_start[b + 1] - t0);
+    const int p_first = seq_pos0[b] + tile * AP_TQ, p_last = grouped ? p_first : p_first + nq - 1;
     pdl_wait();
     q = pdl_fresh(q);
     k_cache = pdl_fresh(k_cache);
@@ -240,7 +243,7 @@ attention_pool_kernel(const TQ* __restrict__ q, long long ldq, const TC* __restr
     gate = pdl_fresh(gate);
     for (int i = tid; i < AP_TQ * d; i += AP_THREADS) {
         const int qi = i / d, c = i - qi * d;
-        Qs[i] = qi < nq ? to_f32(q[(size_t)(t0 + qi) * ldq + (size_t)h * d + c]) : 0.0f;
+        Qs[i] = qi < nq ? to_f32(q[(size_t)(grouped ? t0 : t0 + qi) * ldq + (size_t)(grouped ? h0 + qi : h0) * d + c]) : 0.0f;
     }
     // the keys of this tile, as one list: pooled blocks 0 .. nb - 1, then tokens j_lo .. p_last, in tiles of AP_TK
     const int nb = (P > 0 && window > 0 && p_last - window + 1 >= P) ? (p_last - window + 1) / P : 0;
@@ -293,13 +296,14 @@ attention_pool_kernel(const TQ* __restrict__ q, long long ldq, const TC* __restr
             const int qi = qg + 4 * a;
             float wgt = 0.0f;
             if (qi < nq && lane < nk && pages[lane] >= 0) {
-                const int p = p_first + qi, key = k0 + lane;
+                const int p = grouped ? p_first : p_first + qi, key = k0 + lane;
                 const bool seen = pooled ? (key * P + P - 1 <= p - window) : (key <= p && (window <= 0 || p - key < window));
                 if (seen) {
                     const float* qr = Qs + qi * d;
                     const float* kr = Ks + lane * (d + 1);
                     float dot = 0.0f;
                     for (int c = 0; c < d; c++) dot = fmaf(qr[c], kr[c], dot);
+                    const float bias = head_bias != nullptr ? head_bias[grouped ? h0 + qi : h0] : 0.0f;
                     wgt = 1.0f / (1.0f + expf(-(dot * scale + bias)));
                 }
             }
@@ -327,12 +331,12 @@ attention_pool_kernel(const TQ* __restrict__ q, long long ldq, const TC* __restr
     for (int a = 0; a < 4; a++) {
         const int qi = qg * 4 + a;
         if (qi >= nq) continue;
-        const int t = t0 + qi;
+        const int t = grouped ? t0 : t0 + qi;
 #pragma unroll
         for (int m = 0; m < AP_MAX_DIM / 32; m++) {
             const int c = lane + 32 * m;
             if (c >= dv) continue;
-            const size_t col = (size_t)h * dv + c;
+            const size_t col = (size_t)(grouped ? h0 + qi : h0) * dv + c;
             if (splits == 1 && part == 0) {
                 float v = acc[a][m];
                 if (gate != nullptr) v *= 1.0f / (1.0f + expf(-gate[(size_t)t * ldg + col]));
@@ -370,7 +374,7 @@ extern "C" int hb_attention_pool(const void* q, int q_dtype, long long ldq, cons
                                  const int* seq_start, const int* seq_pos0, int n_seqs, int q_tiles, const float* head_bias,
                                  const float* gate, long long ldg, void* out, int out_dtype, long long ldo, float* partial,
                                  int n_tokens, int n_heads, int n_kv_heads, int head_dim, int v_dim, float scale, int window,
-                                 int pool, int n_pages_tok, int n_pages_pool, int splits, int part, int* status, void* stream) {
+                                 int pool, int n_pages_tok, int n_pages_pool, int splits, int part, int grouped, int* status, void* stream) {
     if (n_tokens == 0) return 0;
     HB_REQUIRE(n_tokens > 0 && n_seqs > 0 && q_tiles > 0 && n_heads > 0 && n_kv_heads > 0 && n_heads % n_kv_heads == 0, "attention_pool: bad sizes");
     HB_REQUIRE(hb_attention_pool_supported(head_dim, v_dim), "attention_pool: head sizes %d / %d (up to %d are built)", head_dim, v_dim, AP_MAX_DIM);
@@ -380,7 +384,8 @@ extern "C" int hb_attention_pool(const void* q, int q_dtype, long long ldq, cons
     HB_REQUIRE(part == 0 || (part == 1 && splits == 1 && pool > 0), "attention_pool: the pooled blocks alone are one range");
     cudaStream_t s = (cudaStream_t)stream;
     const size_t smem = ap_smem_bytes(head_dim, v_dim);
-    dim3 grid(q_tiles, n_heads, splits);
+    HB_REQUIRE(!grouped || (n_heads / n_kv_heads <= AP_TQ && q_tiles == n_seqs && n_tokens == n_seqs), "attention_pool: rows by key/value head need one token per sequence and groups of up to %d heads", AP_TQ);
+    dim3 grid(q_tiles, grouped ? n_kv_heads : n_heads, splits);
 #define HB_AP(TQ, TC, TO)                                                                                                                  \
     do {                                                                                                                                   \
         static bool done[HB_MAX_DEVICES] = {};                                                                                             \
@@ -394,7 +399,7 @@ extern "C" int hb_attention_pool(const void* q, int q_dtype, long long ldq, cons
         hb_launch(attention_pool_kernel<TQ, TC, TO>, dim3(grid), dim3(AP_THREADS), smem, s, (const TQ*)q, ldq, (const TC*)k_cache,         \
                   (const TC*)v_cache, pk_cache, pv_cache, pt_tok, pt_pool, pt_width, seq_start, seq_pos0, n_seqs, head_bias, gate, ldg,    \
                   (TO*)out, ldo, partial, n_tokens, n_heads, n_kv_heads, head_dim, v_dim, scale, window, pool, n_pages_tok, n_pages_pool,  \
-                  splits, part, status);                                                                                                   \
+                  splits, part, grouped, status);                                                                                          \
     } while (0)
     if (q_dtype == HB_BF16 && cache_dtype == HB_BF16 && out_dtype == HB_BF16) HB_AP(bf16, bf16, bf16);
     else if (q_dtype == HB_F32 && cache_dtype == HB_F32 && out_dtype == HB_F32) HB_AP(float, float, float);

@@ -54,15 +54,55 @@ decay_memory_kernel(const float* __restrict__ proj, long long ldp, const float* 
     for (int base = 0; base < n_all; base += DM_CHUNK) {
         const int n = min(DM_CHUNK, n_all - base);
         __syncthreads();                               // the chunk before has been read; the state is in place
-        for (int i = tid; i < n * d; i += DM_THREADS) {
-            const int j = i / d, c = i - j * d;
-            const float* row = proj + (size_t)(start + base + j) * ldp;
-            Qs[j * (d + 1) + c] = dm_act(row[qo + c], act);
-            Ks[j * (d + 1) + c] = dm_act(row[ko + c], act);
-        }
-        for (int i = tid; i < n * DM_COLS; i += DM_THREADS) {
-            const int j = i >> 5, c = i & 31;
-            Vs[i] = (c0 + c < dv) ? dm_act(proj[(size_t)(start + base + j) * ldp + vo + c0 + c], act) : 0.0f;
+        if (((d | dv | c0) & 3) == 0 && (ldp & 3) == 0 && ((qo | ko | vo) & 3) == 0 && ((uintptr_t)proj & 15) == 0) {
+            // 16-byte loads, all of a thread's loads in flight before the first activation
+            const int cpr = d / 4, total = 2 * n * cpr;                     // q chunks, then k chunks
+            for (int base0 = 0; base0 < total; base0 += DM_THREADS * 4) {
+                float4 raw[4];
+                int at[4];
+#pragma unroll
+                for (int u = 0; u < 4; u++) {
+                    const int i = base0 + u * DM_THREADS + tid;
+                    at[u] = -1;
+                    if (i < total) {
+                        const int which = i >= n * cpr, r = i - which * n * cpr;
+                        const int j = r / cpr, ch = r - j * cpr;
+                        raw[u] = *reinterpret_cast<const float4*>(proj + (size_t)(start + base + j) * ldp + (which ? ko : qo) + ch * 4);
+                        at[u] = which * DM_CHUNK * (d + 1) + j * (d + 1) + ch * 4;
+                    }
+                }
+#pragma unroll
+                for (int u = 0; u < 4; u++) {
+                    if (at[u] < 0) continue;
+                    float* dst = Qs + at[u];                                // Ks follows Qs
+                    dst[0] = dm_act(raw[u].x, act);
+                    dst[1] = dm_act(raw[u].y, act);
+                    dst[2] = dm_act(raw[u].z, act);
+                    dst[3] = dm_act(raw[u].w, act);
+                }
+            }
+            const int wv = min(DM_COLS, dv - c0) / 4;                       // whole chunks of this slice's value columns
+            for (int i = tid; i < n * (DM_COLS / 4); i += DM_THREADS) {
+                const int j = i / (DM_COLS / 4), ch = i - j * (DM_COLS / 4);
+                float4 v = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                if (ch < wv) v = *reinterpret_cast<const float4*>(proj + (size_t)(start + base + j) * ldp + vo + c0 + ch * 4);
+                float* dst = Vs + j * DM_COLS + ch * 4;
+                dst[0] = ch < wv ? dm_act(v.x, act) : 0.0f;
+                dst[1] = ch < wv ? dm_act(v.y, act) : 0.0f;
+                dst[2] = ch < wv ? dm_act(v.z, act) : 0.0f;
+                dst[3] = ch < wv ? dm_act(v.w, act) : 0.0f;
+            }
+        } else {
+            for (int i = tid; i < n * d; i += DM_THREADS) {
+                const int j = i / d, c = i - j * d;
+                const float* row = proj + (size_t)(start + base + j) * ldp;
+                Qs[j * (d + 1) + c] = dm_act(row[qo + c], act);
+                Ks[j * (d + 1) + c] = dm_act(row[ko + c], act);
+            }
+            for (int i = tid; i < n * DM_COLS; i += DM_THREADS) {
+                const int j = i >> 5, c = i & 31;
+                Vs[i] = (c0 + c < dv) ? dm_act(proj[(size_t)(start + base + j) * ldp + vo + c0 + c], act) : 0.0f;
+            }
         }
         __syncthreads();
         // a[j][s] = decay^(j-s) q_j . k_s for s <= j

@@ -152,6 +152,7 @@ selective_scan_kernel(const TU* __restrict__ u, long long ldu, const float* __re
             ds[i] = cc < I ? ss_softplus(dt_raw[t * lddt + cc] + b_dt[cc]) : 0.0f;
         }
         __syncthreads();
+#pragma unroll 4
         for (int j = 0; j < nt; j++) {
             const float* row = rows + j * wrow;
             const float dt = ds[j * CH + ch];

@@ -85,7 +85,7 @@ _SIGNATURES = {
                        _c_int, _c_int, _c_int, _c_int, _c_ptr, _c_ptr],
     "hb_attention_pool": [_c_ptr, _c_int, _c_ll, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_int,
                           _c_int, _c_ptr, _c_ptr, _c_ll, _c_ptr, _c_int, _c_ll, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float,
-                          _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr, _c_ptr],
+                          _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr, _c_ptr],
     "hb_attention_pool_prefill": [_c_ptr, _c_ll, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ll, _c_ptr, _c_ll,
                                   _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_int, _c_ptr, _c_ptr],
     "hb_decay_memory": [_c_ptr, _c_ll, _c_ptr, _c_ptr, _c_ll, _c_ptr, _c_ptr, _c_ptr, _c_ll, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr],
@@ -1094,7 +1094,7 @@ class Ops:
                 share = workspace.buffer("attention_pool.pooled_share", (workspace_rows(workspace, T), heads * v_dim), torch.float32)[:T]
                 self._call("hb_attention_pool", q.data_ptr(), _code(q), _rows(q, "queries"), cache.k.data_ptr(), cache.v.data_ptr(),
                            _code(cache.k), *common, tiles, bias_ptr, None, 0, out.data_ptr(), _code(out), _rows(out, "attention output"),
-                           share.data_ptr(), *sizes, 1, 1, self.status.data_ptr(), self._stream())
+                           share.data_ptr(), *sizes, 1, 1, 0, self.status.data_ptr(), self._stream())
                 self.launches += 1
             self._call("hb_attention_pool_prefill", q.data_ptr(), _rows(q, "queries"), cache.k.data_ptr(), cache.v.data_ptr(), pt.data_ptr(),
                        pt.shape[1], step.seq_start.data_ptr(), step.seq_pos0.data_ptr(), bias_ptr,
@@ -1104,7 +1104,9 @@ class Ops:
                        cache.k.shape[0], self.status.data_ptr(), self._stream())
             self.launches += 1
             return
-        splits = self.attention_pool_splits(step, heads, window, pool)
+        # one token per sequence: a block's rows are the query heads of a key/value head, which are then staged once per group
+        grouped = 1 if (step.is_decode and heads // kv_heads <= self.ATTENTION_POOL_TILE) else 0
+        splits = self.attention_pool_splits(step, kv_heads if grouped else heads, window, pool)
         partial = None
         if splits > 1:
             # the same buffer for every step of a shape: a captured graph holds its address
@@ -1112,7 +1114,7 @@ class Ops:
         self._call("hb_attention_pool", q.data_ptr(), _code(q), _rows(q, "queries"), cache.k.data_ptr(), cache.v.data_ptr(),
                    _code(cache.k), *common, tiles, bias_ptr, gate.data_ptr() if gate is not None else None,
                    _rows(gate, "gate") if gate is not None else 0, out.data_ptr(), _code(out), _rows(out, "attention output"),
-                   partial.data_ptr() if partial is not None else None, *sizes, splits, 0, self.status.data_ptr(), self._stream())
+                   partial.data_ptr() if partial is not None else None, *sizes, splits, 0, grouped, self.status.data_ptr(), self._stream())
         self.launches += 1 if splits == 1 else 2
 
     # ------------------------------------------------------------------ matrix memory with a fixed decay
