@@ -195,10 +195,13 @@ int hb_gated_norm(const float* o, long long ldi, const float* gate, long long ld
 int hb_conv_act(const float* x, long long ldx, const float* conv_w, const float* conv_b, int taps, float* state, long long state_stride,
                 const int* state_slots, const int* seq_start, void* out, int out_dtype, long long ldo, int n_seqs, int max_new, int C,
                 int act, void* stream);
+// chunk_len 0: one block walks a sequence's tokens; else chunks of chunk_len run side by side in three launches and need
+// carry: n_seqs * max_chunks * inner * (2 * n_state + 1) floats (max_chunks = the most chunks a sequence has)
 int hb_selective_scan(const void* u, int u_dtype, long long ldu, const float* bc, long long ldb, const float* z, long long ldz,
                       const float* dt_raw, long long lddt, const float* b_dt, const float* a_log, const float* dvec, float* state,
                       long long state_stride, const int* state_slots, const int* seq_start, void* out, int out_dtype, long long ldo,
-                      int n_seqs, int inner, int n_state, void* stream);
+                      int n_seqs, int inner, int n_state, int chunk_len, int max_chunks, float* carry, long long carry_floats,
+                      void* stream);
 // Mixture of experts (moe.cu)
 int hb_moe_route(const void* h, int h_dtype, long long ldh, const float* w_router, int* experts, float* weights, int n_tokens, int width,
                  int n_experts, int top, void* stream);

@@ -7,7 +7,7 @@
 //   S'  = decay^n S0 + sum_s decay^(n-1-s) k_s v_s^T                        (n tokens in the chunk)
 // so one pass over the state serves up to DM_CHUNK tokens; a chunk of one token is the recurrence
 // itself (decode steps).  Only non-negative powers of the decay appear, nothing is divided.  One
-// block per (slice of 32 value columns, head, sequence), everything in 32-bit FP32-pipe code.
+// block per (slice of DM_COLS value columns, head, sequence), everything in 32-bit FP32-pipe code.
 //
 // gated_norm: out = o / sqrt(mean(o^2) + eps) * w * sigmoid(gate) * out_scale over each row (all
 // heads together), rounded once for the output product.
@@ -16,7 +16,8 @@
 
 #define DM_THREADS 256
 #define DM_CHUNK 32
-#define DM_COLS 32
+#define DM_COLS 16           // value columns a block owns: narrow slices, so that one sequence's heads fill the device
+#define DM_GROUPS (DM_THREADS / DM_COLS)
 #define DM_MAX_DIM 256
 
 static size_t dm_smem_bytes(int d) {
@@ -39,7 +40,7 @@ decay_memory_kernel(const float* __restrict__ proj, long long ldp, const float* 
     float* Ss = As + DM_CHUNK * (DM_CHUNK + 1);
     float* pw = Ss + d * DM_COLS;
     const int tid = threadIdx.x, c0 = blockIdx.x * DM_COLS, h = blockIdx.y, b = blockIdx.z;
-    const int lane = tid & 31, grp = tid >> 5;          // column lane, 8 groups
+    const int lane = tid % DM_COLS, grp = tid / DM_COLS;   // column lane, DM_GROUPS groups
     const int col = c0 + lane;
     const bool live = col < dv;
     const int start = seq_start[b], n_all = seq_start[b + 1] - start;
@@ -49,7 +50,7 @@ decay_memory_kernel(const float* __restrict__ proj, long long ldp, const float* 
     proj = pdl_fresh(proj);
     state = pdl_fresh(state);
     float* S = state + (size_t)state_slots[b] * state_stride + (size_t)h * d * dv;
-    for (int i = grp; i < d; i += 8) Ss[i * DM_COLS + lane] = live ? S[(size_t)i * dv + col] : 0.0f;
+    for (int i = grp; i < d; i += DM_GROUPS) Ss[i * DM_COLS + lane] = live ? S[(size_t)i * dv + col] : 0.0f;
     const long long qo = (long long)h * d, ko = (long long)H * d + (long long)h * d, vo = (long long)2 * H * d + (long long)h * dv;
     for (int base = 0; base < n_all; base += DM_CHUNK) {
         const int n = min(DM_CHUNK, n_all - base);
@@ -100,7 +101,7 @@ decay_memory_kernel(const float* __restrict__ proj, long long ldp, const float* 
                 Ks[j * (d + 1) + c] = dm_act(row[ko + c], act);
             }
             for (int i = tid; i < n * DM_COLS; i += DM_THREADS) {
-                const int j = i >> 5, c = i & 31;
+                const int j = i / DM_COLS, c = i % DM_COLS;
                 Vs[i] = (c0 + c < dv) ? dm_act(proj[(size_t)(start + base + j) * ldp + vo + c0 + c], act) : 0.0f;
             }
         }
@@ -119,8 +120,8 @@ decay_memory_kernel(const float* __restrict__ proj, long long ldp, const float* 
             As[j * (DM_CHUNK + 1) + s] = a;
         }
         __syncthreads();
-        // o[j][col]: tokens j = grp, grp + 8, ...
-        for (int j = grp; j < n; j += 8) {
+        // o[j][col]: tokens j = grp, grp + DM_GROUPS, ...
+        for (int j = grp; j < n; j += DM_GROUPS) {
             const float* qr = Qs + j * (d + 1);
             float from_state = 0.0f;
             for (int i = 0; i < d; i++) from_state = fmaf(Ss[i * DM_COLS + lane], qr[i], from_state);
@@ -130,8 +131,8 @@ decay_memory_kernel(const float* __restrict__ proj, long long ldp, const float* 
             if (live) out[(size_t)(start + base + j) * ldo + (size_t)h * dv + col] = o;
         }
         __syncthreads();                               // every reader of the old state is done
-        // S[i][col] = decay^n S[i][col] + sum_s decay^(n-1-s) k_s[i] v_s[col]: rows i = grp, grp + 8, ...
-        for (int i = grp; i < d; i += 8) {
+        // S[i][col] = decay^n S[i][col] + sum_s decay^(n-1-s) k_s[i] v_s[col]: rows i = grp, grp + DM_GROUPS, ...
+        for (int i = grp; i < d; i += DM_GROUPS) {
             float acc = Ss[i * DM_COLS + lane] * pw[n];
             for (int s = 0; s < n; s++) acc = fmaf(Ks[s * (d + 1) + i] * pw[n - 1 - s], Vs[s * DM_COLS + lane], acc);
             Ss[i * DM_COLS + lane] = acc;
@@ -139,7 +140,7 @@ decay_memory_kernel(const float* __restrict__ proj, long long ldp, const float* 
     }
     __syncthreads();
     if (live)
-        for (int i = grp; i < d; i += 8) S[(size_t)i * dv + col] = Ss[i * DM_COLS + lane];
+        for (int i = grp; i < d; i += DM_GROUPS) S[(size_t)i * dv + col] = Ss[i * DM_COLS + lane];
 }
 
 extern "C" int hb_decay_memory(const float* proj, long long ldp, const float* decay, float* state, long long state_stride,

@@ -13,6 +13,12 @@
 // of SS_LANES threads owns a channel (state index n = lane, lane + SS_LANES, ...); a block owns
 // SS_CH channels of one sequence and walks its tokens in order, SS_TOK tokens of inputs staged
 // in shared memory at a time.  The state is read once and written once per step.
+//
+// Steps that bring many tokens to a sequence cut its tokens into chunks of `chunk_len` and run three launches, so that the
+// chunks run side by side instead of one block walking thousands of tokens: (1) every chunk from a zero state, without
+// outputs: its final state L and the sum of its step sizes; (2) scan_carry: chunk by chunk, S_start[k + 1] = exp(A sum dt_k)
+// S_start[k] + L_k (the recurrence is linear in S, and the product of a chunk's decays is the exponential of the sum), which
+// also leaves the sequence's new state; (3) every chunk again from its S_start, with outputs.  Same sums, another order.
 #include "api.h"
 #include "common.cuh"
 
@@ -96,6 +102,21 @@ extern "C" int hb_conv_act(const float* x, long long ldx, const float* conv_w, c
 #define SS_MAX_PER 8        // state values a thread holds: state sizes up to SS_MAX_PER * lanes
 
 __device__ __forceinline__ float ss_softplus(float z) { return z > 20.0f ? z : log1pf(expf(z)); }
+// exp(x) - 1 for x <= 0.  FAST (the bfloat16 path): six terms of the series near zero (remainder below 1e-9 of x), the hardware's
+// exp2 elsewhere, where the decay is far from one and an error of 2e-7 of it does not build up; else the library's expm1.
+template <bool FAST>
+__device__ __forceinline__ float ss_expm1(float x) {
+    if (!FAST) return expm1f(x);
+    if (x > -0.125f) {
+        float p = fmaf(x, 1.0f / 720.0f, 1.0f / 120.0f);
+        p = fmaf(p, x, 1.0f / 24.0f);
+        p = fmaf(p, x, 1.0f / 6.0f);
+        p = fmaf(p, x, 0.5f);
+        p = fmaf(p, x, 1.0f);
+        return p * x;
+    }
+    return __expf(x) - 1.0f;
+}
 
 template <typename TU, typename TO, int LANES>
 __global__ void __launch_bounds__(SS_THREADS)
@@ -103,7 +124,10 @@ selective_scan_kernel(const TU* __restrict__ u, long long ldu, const float* __re
                       const float* __restrict__ z, long long ldz, const float* __restrict__ dt_raw, long long lddt,
                       const float* __restrict__ b_dt, const float* __restrict__ a_log, const float* __restrict__ dvec,
                       float* __restrict__ state, long long state_stride, const int* __restrict__ state_slots,
-                      const int* __restrict__ seq_start, TO* __restrict__ out, long long ldo, int I, int N) {
+                      const int* __restrict__ seq_start, TO* __restrict__ out, long long ldo, int I, int N, int mode, int chunk_len,
+                      int max_chunks, float* __restrict__ carry_L, float* __restrict__ carry_dt, const float* __restrict__ carry_S0) {
+    // mode 0: the whole step from the sequence's state; 1: chunk blockIdx.z from zeros, no outputs, L and sum dt out;
+    // 3: chunk blockIdx.z from carry_S0, with outputs (the state was written by scan_carry)
     pdl_trigger();
     constexpr int CH = SS_THREADS / LANES;             // channels per block
     extern __shared__ float ss_smem[];
@@ -114,9 +138,14 @@ selective_scan_kernel(const TU* __restrict__ u, long long ldu, const float* __re
     const int tid = threadIdx.x, lane = tid % LANES, ch = tid / LANES;
     const int c = blockIdx.x * CH + ch, b = blockIdx.y;
     const bool live = c < I;
-    const int start = seq_start[b], n_all = seq_start[b + 1] - start;
+    const int n_seq = seq_start[b + 1] - seq_start[b];
+    const int t_lo = mode == 0 ? 0 : (int)blockIdx.z * chunk_len;
+    if (t_lo >= n_seq && mode != 0) return;
+    const int start = seq_start[b] + t_lo, n_all = mode == 0 ? n_seq : min(chunk_len, n_seq - t_lo);
+    const size_t carry_at = ((size_t)b * max_chunks + blockIdx.z) * I + (c < I ? c : 0);
     const int wrow = 2 * N;
     float A[SS_MAX_PER], S[SS_MAX_PER];
+    float sum_dt = 0.0f;
 #pragma unroll
     for (int k = 0; k < SS_MAX_PER; k++) {
         const int n = lane + k * LANES;
@@ -129,11 +158,13 @@ selective_scan_kernel(const TU* __restrict__ u, long long ldu, const float* __re
     z = pdl_fresh(z);
     dt_raw = pdl_fresh(dt_raw);
     state = pdl_fresh(state);
+    carry_S0 = pdl_fresh(carry_S0);
     float* srow = state + (size_t)state_slots[b] * state_stride + (size_t)(live ? c : 0) * N;
 #pragma unroll
     for (int k = 0; k < SS_MAX_PER; k++) {
         const int n = lane + k * LANES;
-        S[k] = (live && n < N) ? srow[n] : 0.0f;
+        S[k] = 0.0f;
+        if (live && n < N && mode != 1) S[k] = mode == 0 ? srow[n] : carry_S0[carry_at * N + n];
     }
     for (int base = 0; base < n_all; base += SS_TOK) {
         const int nt = min(SS_TOK, n_all - base);
@@ -158,6 +189,7 @@ selective_scan_kernel(const TU* __restrict__ u, long long ldu, const float* __re
             const float dt = ds[j * CH + ch];
             const float uv = us[j * CH + ch];
             const float dtu = dt * uv;
+            sum_dt += dt;
             float y = 0.0f;
 #pragma unroll
             for (int k = 0; k < SS_MAX_PER; k++) {
@@ -165,10 +197,11 @@ selective_scan_kernel(const TU* __restrict__ u, long long ldu, const float* __re
                 if (n < N) {
                     // S <- S + (exp(dt A) - 1) S + dt u B: with decays close to one, exp() rounded to 32 bits is off by up to
                     // 6e-8 of 1, i.e. by percents of the distance to one, and that error would grow with every token
-                    S[k] = fmaf(expm1f(dt * A[k]), S[k], fmaf(dtu, row[n], S[k]));
+                    S[k] = fmaf(ss_expm1<sizeof(TU) == 2>(dt * A[k]), S[k], fmaf(dtu, row[n], S[k]));
                     y = fmaf(S[k], row[N + n], y);
                 }
             }
+            if (mode == 1) continue;                   // only the chunk's final state is wanted
 #pragma unroll
             for (int o = LANES / 2; o > 0; o >>= 1) y += __shfl_xor_sync(0xffffffffu, y, o, LANES);
             if (lane == 0 && live) {
@@ -176,43 +209,114 @@ selective_scan_kernel(const TU* __restrict__ u, long long ldu, const float* __re
             }
         }
     }
-    if (live) {
+    if (live && mode != 3) {
 #pragma unroll
         for (int k = 0; k < SS_MAX_PER; k++) {
             const int n = lane + k * LANES;
-            if (n < N) srow[n] = S[k];
+            if (n < N) (mode == 0 ? srow : carry_L + carry_at * N)[n] = S[k];
         }
+        if (mode == 1 && lane == 0) carry_dt[carry_at] = sum_dt;
     }
 }
 
-static int ss_lanes(int N) { return N <= 4 ? 4 : N <= 8 ? 8 : N <= 16 ? 16 : 32; }
+// S_start of every chunk and the sequence's new state: one thread per (sequence, channel, state index)
+__global__ void __launch_bounds__(256)
+scan_carry_kernel(const float* __restrict__ a_log, const float* __restrict__ carry_L, const float* __restrict__ carry_dt,
+                  float* __restrict__ carry_S0, float* __restrict__ state, long long state_stride, const int* __restrict__ state_slots,
+                  const int* __restrict__ seq_start, int I, int N, int chunk_len, int max_chunks) {
+    pdl_trigger();
+    pdl_wait();
+    carry_L = pdl_fresh(carry_L);
+    carry_dt = pdl_fresh(carry_dt);
+    state = pdl_fresh(state);
+    const int b = blockIdx.y;
+    const long long i = (long long)blockIdx.x * 256 + threadIdx.x;
+    if (i >= (long long)I * N) return;
+    const int c = (int)(i / N);
+    const int chunks = (seq_start[b + 1] - seq_start[b] + chunk_len - 1) / chunk_len;
+    const float A = -expf(a_log[i]);
+    float* sp = state + (size_t)state_slots[b] * state_stride + i;
+    float S = *sp;
+    for (int k = 0; k < chunks; k++) {
+        const size_t at = ((size_t)b * max_chunks + k) * I;
+        carry_S0[at * N + i] = S;
+        S = fmaf(expm1f(A * carry_dt[at + c]), S, S) + carry_L[at * N + i];
+    }
+    *sp = S;
+}
+
+// Lanes per channel: four state values a thread where the state is large enough (fewer instructions per channel: the loads,
+// the loop and the shuffle sum are shared by a thread's values), but more lanes while the grid has fewer than two blocks per
+// SM: a block's walk is a chain of dependent steps and of staging loads that nothing hides but other blocks (measured at
+// 8192 channels of 16 state values, 2048 tokens: 1.33 ms with 16 lanes and 512 blocks, 1.77 ms with 4 lanes and 128 blocks).
+static int ss_lanes(int N, int inner, long long grids) {
+    int full = N <= 4 ? 4 : N <= 8 ? 8 : N <= 16 ? 16 : 32;               // one value a lane (up to SS_MAX_PER beyond 32)
+    int lanes = full / 4 < 4 ? 4 : full / 4;
+    while (lanes * SS_MAX_PER < N) lanes *= 2;
+    int sms = 148;
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, hb_device_slot());
+    while (lanes < full && (long long)((inner + SS_THREADS / lanes - 1) / (SS_THREADS / lanes)) * grids < 2 * sms) lanes *= 2;
+    return lanes;
+}
 
 extern "C" int hb_selective_scan(const void* u, int u_dtype, long long ldu, const float* bc, long long ldb, const float* z, long long ldz,
                                  const float* dt_raw, long long lddt, const float* b_dt, const float* a_log, const float* dvec, float* state,
                                  long long state_stride, const int* state_slots, const int* seq_start, void* out, int out_dtype,
-                                 long long ldo, int n_seqs, int inner, int n_state, void* stream) {
+                                 long long ldo, int n_seqs, int inner, int n_state, int chunk_len, int max_chunks, float* carry,
+                                 long long carry_floats, void* stream) {
     if (n_seqs == 0) return 0;
     HB_REQUIRE(n_seqs > 0 && n_seqs <= 65535 && inner > 0 && n_state > 0, "selective_scan: bad sizes");
     HB_REQUIRE(n_state <= SS_MAX_PER * 32, "selective_scan: state size %d (up to %d is built)", n_state, SS_MAX_PER * 32);
     HB_REQUIRE(ldb >= 2 * n_state && ldu >= inner && ldz >= inner && lddt >= inner && ldo >= inner && state_stride >= (long long)inner * n_state,
                "selective_scan: rows are too short");
     HB_REQUIRE(u_dtype == out_dtype && (u_dtype == HB_BF16 || u_dtype == HB_F32), "selective_scan: unsupported dtypes %d -> %d", u_dtype, out_dtype);
-    const int lanes = ss_lanes(n_state), ch = SS_THREADS / lanes;
+    const long long per = (long long)n_seqs * max_chunks * inner;               // (sequence, chunk, channel) triples
+    HB_REQUIRE(chunk_len == 0 || (chunk_len > 0 && max_chunks > 0 && max_chunks <= 65535 && carry != nullptr && carry_floats >= per * (2 * n_state + 1)),
+               "selective_scan: chunks need (2 * state + 1) floats per sequence, chunk and channel");
+    float* carry_L = carry;
+    float* carry_S0 = carry ? carry + per * n_state : nullptr;
+    float* carry_dt = carry ? carry + 2 * per * n_state : nullptr;
+    const int lanes = ss_lanes(n_state, inner, (long long)n_seqs * (chunk_len ? max_chunks : 1)), ch = SS_THREADS / lanes;
     const size_t smem = sizeof(float) * ((size_t)SS_TOK * 2 * n_state + 3 * SS_TOK * ch);
-    dim3 grid((inner + ch - 1) / ch, n_seqs);
+    HB_REQUIRE(smem <= 200 * 1024, "selective_scan: state size %d needs too much shared memory", n_state);
     cudaStream_t s = (cudaStream_t)stream;
-#define HB_SS(TU, TO, L)                                                                                                                  \
-    hb_launch(selective_scan_kernel<TU, TO, L>, dim3(grid), dim3(SS_THREADS), smem, s, (const TU*)u, ldu, bc, ldb, z, ldz, dt_raw, lddt,  \
-              b_dt, a_log, dvec, state, state_stride, state_slots, seq_start, (TO*)out, ldo, inner, n_state)
-#define HB_SS_L(TU, TO)                                                                          \
+#define HB_SS(TU, TO, L, MODE)                                                                                                            \
+    if (smem > 48 * 1024) {                                                                                                               \
+        static bool done[HB_MAX_DEVICES] = {};                                                                                            \
+        const int slot = hb_device_slot();                                                                                                \
+        if (!done[slot]) {                                                                                                                \
+            cudaError_t e = cudaFuncSetAttribute(selective_scan_kernel<TU, TO, L>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024); \
+            if (e != cudaSuccess) return hb_fail("selective_scan: shared memory: %s", cudaGetErrorString(e));                             \
+            done[slot] = true;                                                                                                            \
+        }                                                                                                                                 \
+    }                                                                                                                                     \
+    hb_launch(selective_scan_kernel<TU, TO, L>, dim3((inner + ch - 1) / ch, n_seqs, MODE == 0 ? 1 : max_chunks), dim3(SS_THREADS), smem, s,  \
+              (const TU*)u, ldu, bc, ldb, z, ldz, dt_raw, lddt, b_dt, a_log, dvec, state, state_stride, state_slots, seq_start, (TO*)out,    \
+              ldo, inner, n_state, MODE, chunk_len, max_chunks, carry_L, carry_dt, (const float*)carry_S0)
+#define HB_SS_L(TU, TO, MODE)                                                                    \
     switch (lanes) {                                                                             \
-        case 4: HB_SS(TU, TO, 4); break;                                                         \
-        case 8: HB_SS(TU, TO, 8); break;                                                         \
-        case 16: HB_SS(TU, TO, 16); break;                                                       \
-        default: HB_SS(TU, TO, 32); break;                                                       \
+        case 4: HB_SS(TU, TO, 4, MODE); break;                                                   \
+        case 8: HB_SS(TU, TO, 8, MODE); break;                                                   \
+        case 16: HB_SS(TU, TO, 16, MODE); break;                                                 \
+        default: HB_SS(TU, TO, 32, MODE); break;                                                 \
     }
-    if (u_dtype == HB_BF16) { HB_SS_L(bf16, bf16) } else { HB_SS_L(float, float) }
+#define HB_SS_M(MODE)                                                                            \
+    do {                                                                                         \
+        if (u_dtype == HB_BF16) { HB_SS_L(bf16, bf16, MODE) } else { HB_SS_L(float, float, MODE) } \
+    } while (0)
+    if (chunk_len == 0) {
+        HB_SS_M(0);
+        return hb_check_launch("selective_scan");
+    }
+    HB_SS_M(1);
+    if (hb_check_launch("selective_scan (chunks from zero)")) return 1;
+    const long long elems = (long long)inner * n_state;
+    hb_launch(scan_carry_kernel, dim3((unsigned)((elems + 255) / 256), n_seqs), dim3(256), 0, s, a_log, (const float*)carry_L,
+              (const float*)carry_dt, carry_S0, state, state_stride, state_slots, seq_start, inner, n_state, chunk_len, max_chunks);
+    if (hb_check_launch("scan_carry")) return 1;
+    HB_SS_M(3);
+#undef HB_SS_M
 #undef HB_SS_L
 #undef HB_SS
-    return hb_check_launch("selective_scan");
+    return hb_check_launch("selective_scan (chunks with outputs)");
 }

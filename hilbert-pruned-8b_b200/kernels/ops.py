@@ -93,7 +93,7 @@ _SIGNATURES = {
     "hb_conv_act": [_c_ptr, _c_ll, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_ll, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_ll, _c_int, _c_int, _c_int,
                     _c_int, _c_ptr],
     "hb_selective_scan": [_c_ptr, _c_int, _c_ll, _c_ptr, _c_ll, _c_ptr, _c_ll, _c_ptr, _c_ll, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ll, _c_ptr,
-                          _c_ptr, _c_ptr, _c_int, _c_ll, _c_int, _c_int, _c_int, _c_ptr],
+                          _c_ptr, _c_ptr, _c_int, _c_ll, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr, _c_ll, _c_ptr],
     "hb_moe_route": [_c_ptr, _c_int, _c_ll, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_ptr],
     "hb_moe_plan": [_c_ptr, _c_int, _c_int, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_ptr],
     "hb_moe_glu": [_c_ptr, _c_int, _c_ll, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_ptr, _c_int, _c_ll, _c_int,
@@ -1164,10 +1164,16 @@ class Ops:
                    _rows(out, "conv_act output"), step.num_seqs, step.max_new, C, self.ACTIVATIONS[activation], self._stream())
         self.launches += 1
 
-    def selective_scan(self, u, bc, z, dt_raw, b_dt, a_log, d_skip, state, step, out, n_state: int) -> None:
+    SCAN_CHUNK_FROM = 128           # steps whose longest portion has at least so many tokens run the scan in chunks side by side
+    SCAN_CHUNK = 64
+
+    def selective_scan(self, u, bc, z, dt_raw, b_dt, a_log, d_skip, state, step, out, n_state: int, workspace=None,
+                       chunked: Optional[bool] = None) -> None:
         """The selective scan over a step's tokens, sequence by sequence: ``bc`` float32 rows ``[B | C]``, ``z`` float32 gate
         input, ``dt_raw`` float32 ``[tokens, inner]`` (the step sizes before bias and softplus), ``u`` and ``out`` in the
-        activations' dtype ``[tokens, inner]``; ``state`` float32 ``[slots, inner * n_state]``."""
+        activations' dtype ``[tokens, inner]``; ``state`` float32 ``[slots, inner * n_state]``.  ``chunked`` (default: steps that
+        bring ``SCAN_CHUNK_FROM`` tokens or more to a sequence while channels and sequences are too few to fill the device, given
+        a ``workspace``): the tokens of a sequence are cut into chunks that run side by side (three launches)."""
         self._dev(u, bc, z, dt_raw, b_dt, a_log, d_skip, state, out)
         T, inner = u.shape
         if any(t.dtype != torch.float32 for t in (bc, z, dt_raw)) or tuple(z.shape) != (T, inner) or tuple(dt_raw.shape) != (T, inner) \
@@ -1177,12 +1183,22 @@ class Ops:
             raise KernelError("selective_scan: float32 A_log [inner, state] expected")
         if state.dtype != torch.float32 or state.dim() != 2 or state.shape[1] != inner * n_state or state.stride(1) != 1:
             raise KernelError("selective_scan: state must be float32 [slots, inner * state]")
+        if chunked is None:
+            # chunks pay (they walk every token twice) only while one block per group of channels and sequence leaves SMs idle
+            chunked = (workspace is not None and not step.is_decode and step.max_new >= self.SCAN_CHUNK_FROM
+                       and -(-inner // 8) * step.num_seqs < self.sm_count)
+        chunk_len, max_chunks, carry = 0, 0, None
+        if chunked:
+            chunk_len = self.SCAN_CHUNK
+            max_chunks = -(-step.max_new // chunk_len)
+            carry = workspace.buffer("selective_scan.carry", (step.num_seqs * max_chunks * inner * (2 * n_state + 1),), torch.float32)
         self._call("hb_selective_scan", u.data_ptr(), _code(u), _rows(u, "scan input"), bc.data_ptr(), _rows(bc, "scan parameters"),
                    z.data_ptr(), _rows(z, "scan gate"), dt_raw.data_ptr(), _rows(dt_raw, "step sizes"),
                    self._f32_vec(b_dt, inner, "step-size bias"), a_log.data_ptr(), self._f32_vec(d_skip, inner, "skip weight"),
                    state.data_ptr(), state.stride(0), step.state_slots.data_ptr(), step.seq_start.data_ptr(), out.data_ptr(), _code(out),
-                   _rows(out, "scan output"), step.num_seqs, inner, n_state, self._stream())
-        self.launches += 1
+                   _rows(out, "scan output"), step.num_seqs, inner, n_state, chunk_len, max_chunks,
+                   carry.data_ptr() if carry is not None else None, carry.numel() if carry is not None else 0, self._stream())
+        self.launches += 3 if chunked else 1
 
     # ------------------------------------------------------------------ mixture of experts
     def moe_route(self, h, w_router, top: int, experts, weights) -> None:

@@ -98,5 +98,5 @@ class SelectiveScan(Mixer):
             ops.linear(dbc[:, :R], self.w_dt, dt_raw)
             bc = dbc[:, R: R + 2 * N]
         y = ws.buffer("selective_scan.y", (cap, I), self.ctx.dtype)[:T]
-        ops.selective_scan(u, bc, xz[:, I:], dt_raw, self.b_dt, self.a_log, self.d_skip, state[:, self.conv_state:], step, y, N)
+        ops.selective_scan(u, bc, xz[:, I:], dt_raw, self.b_dt, self.a_log, self.d_skip, state[:, self.conv_state:], step, y, N, workspace=ws)
         ops.linear(y, self.w_o, residual, accumulate=accumulate)

@@ -357,8 +357,9 @@ def test_decayed_memory_in_portions_equals_the_recurrence(heads, d, dv):
 @pytest.mark.gpu
 @pytest.mark.parametrize("inner,n_state,dt_rank,taps", [(96, 8, 5, 3), (40, 1, 1, 1), (70, 33, 2, 5), (256, 16, 16, 4), (24, 100, 3, 2)])
 def test_convolution_and_selective_scan_carry_their_state_over_portions(inner, n_state, dt_rank, taps):
-    """Two sequences of unequal lengths fed in portions of 1, 2, ... and of several hundred tokens: the values of the whole
-    sequence at once.  Some channels forget almost nothing (step sizes near zero), some almost everything."""
+    """Two sequences of unequal lengths fed in portions of 1, 2, ... and of several hundred tokens (those run as chunks side by
+    side): the values of the whole sequence at once.  Some channels forget almost nothing (step sizes near zero), some almost
+    everything."""
     require_gpu()
     I, N, R = inner, n_state, dt_rank
     conv_state = (taps - 1) * I
@@ -389,7 +390,8 @@ def test_convolution_and_selective_scan_carry_their_state_over_portions(inner, n
         dbc = (u.double() @ wx.double().cuda().T).float().contiguous()       # the projections themselves are not under test here
         dt_raw = (dbc[:, :R].double() @ wdt.double().cuda().T).float().contiguous()
         y = torch.empty(T, I, device="cuda")
-        ops.selective_scan(u, dbc[:, R:], pin[:, I:2 * I], dt_raw, bdt.cuda(), a_log.cuda(), D.cuda(), state[:, conv_state:], step, y, N)
+        ops.selective_scan(u, dbc[:, R:], pin[:, I:2 * I], dt_raw, bdt.cuda(), a_log.cuda(), D.cuda(), state[:, conv_state:], step, y, N, workspace=ws,
+                           chunked=max(new) >= 128)
         uc, yc, at = u.cpu(), y.cpu(), 0
         for i, n in zip(live, new):
             got_u[i].append(uc[at: at + n])
