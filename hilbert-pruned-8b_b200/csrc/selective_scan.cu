@@ -63,13 +63,45 @@ conv_act_kernel(const float* __restrict__ x, long long ldx, const float* __restr
         return x[(size_t)(start + src) * ldx + c];
     };
     if (!live) return;
-    for (int t = t_begin + tl; t < t_end; t += CA_TL) {
-        float acc = bias;
+    constexpr int PER = CA_RUN / CA_TL, TOP = CA_MAX_TAPS - 1;
+    const int t0 = t_begin + tl * PER, t1 = min(t_end, t0 + PER);
+    if (n <= CA_TL) {
+        // a handful of tokens (decode steps): one token a thread, its inputs read tap by tap
+        const int t = t_begin + tl;
+        if (t < t_end) {
+            float acc = bias;
 #pragma unroll
-        for (int j = 0; j < CA_MAX_TAPS; j++)
-            if (j < taps) acc = fmaf(w[j], input(t - hist + j), acc);
-        if (act == 1) acc = acc / (1.0f + expf(-acc));
-        out[(size_t)(start + t) * ldo + c] = from_f32<TO>(acc);
+            for (int j = 0; j < CA_MAX_TAPS; j++)
+                if (j < taps) acc = fmaf(w[j], input(t - hist + j), acc);
+            if (act == 1) acc = acc / (1.0f + expf(-acc));
+            out[(size_t)(start + t) * ldo + c] = from_f32<TO>(acc);
+        }
+    } else if (t0 < t1) {
+        // a thread walks CA_RUN / CA_TL consecutive tokens and keeps the last inputs in registers, newest at the top: one load
+        // per token; the taps sit at the top of their array likewise, zeros below them
+        float win[CA_MAX_TAPS], wr[CA_MAX_TAPS];
+        float w_now = 0.0f;
+#pragma unroll
+        for (int j = 0; j < CA_MAX_TAPS; j++) {
+            const int back = TOP - j + 1;                  // win[j] is the input `back` tokens before the current one
+            win[j] = back <= hist ? input(t0 - back) : 0.0f;
+            float wv = 0.0f;
+#pragma unroll
+            for (int k = 0; k < CA_MAX_TAPS; k++) wv = (k == hist - back) ? w[k] : wv;
+            wr[j] = back <= hist ? wv : 0.0f;
+            w_now = (j == hist) ? w[j] : w_now;
+        }
+        for (int t = t0; t < t1; t++) {
+            const float xin = x[(size_t)(start + t) * ldx + c];
+            float acc = fmaf(w_now, xin, bias);
+#pragma unroll
+            for (int j = 0; j < CA_MAX_TAPS; j++) acc = fmaf(wr[j], win[j], acc);
+            if (act == 1) acc = acc / (1.0f + expf(-acc));
+            out[(size_t)(start + t) * ldo + c] = from_f32<TO>(acc);
+#pragma unroll
+            for (int j = 0; j < TOP; j++) win[j] = win[j + 1];
+            win[TOP] = xin;
+        }
     }
     if (first && tl == 0)
         for (int j = 0; j < hist; j++) srow[(size_t)j * C + c] = input(n - hist + j);
