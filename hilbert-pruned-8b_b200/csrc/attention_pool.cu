@@ -115,11 +115,11 @@ pool_blocks_kernel(const TC* __restrict__ k_cache, const TC* __restrict__ v_cach
         if (threadIdx.x == 0) hb_note(status, HB_STATUS_PAGE, 1 + b);
         return;
     }
-    const int per = d + dv, total = G * per;
-    for (int i = threadIdx.x; i < total; i += 128) {
-        const int g = i / per, c = i - g * per;
+    const int per = d + dv, g = blockIdx.z;
+    for (int c = threadIdx.x; c < per; c += 128) {
         float sum = 0.0f;
         bool ok = true;
+#pragma unroll 4
         for (int j = 0; j < P; j++) {
             const int pos = e * P + j;
             const int lp = pos / HB_PAGE_TOKENS;
@@ -143,7 +143,8 @@ extern "C" int hb_pool_blocks(const void* k_cache, const void* v_cache, int cach
                               int n_pages_pool, int* status, void* stream) {
     if (n_seqs == 0) return 0;
     HB_REQUIRE(n_seqs > 0 && n_seqs <= 65535 && max_new >= 1 && pool >= 1 && n_kv_heads > 0 && head_dim > 0 && v_dim > 0, "pool_blocks: bad sizes");
-    dim3 grid(max_new / pool + 1, n_seqs);
+    HB_REQUIRE(n_kv_heads <= 65535, "pool_blocks: too many key/value heads");
+    dim3 grid(max_new / pool + 1, n_seqs, n_kv_heads);
     cudaStream_t s = (cudaStream_t)stream;
     if (cache_dtype == HB_BF16)
         hb_launch(pool_blocks_kernel<bf16>, dim3(grid), dim3(128), 0, s, (const bf16*)k_cache, (const bf16*)v_cache, pk_cache, pv_cache, pt_tok,

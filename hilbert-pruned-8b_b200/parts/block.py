@@ -165,17 +165,28 @@ class FilteredPreNormBlock(Block):
         return None
 
 
+class NormAhead(tuple):
+    """What a block's first norm needs so that the block in front can make its output while it adds its last sublayer's
+    result to the stream: ``(weight, offset, eps, out)``, the form of ``Norm.fold_request``.  A type of its own, so that a
+    block only honours requests of blocks that will understand what it answers with (``NORMED``)."""
+
+
+NORMED = "normed"       # what such a block returns when it has written the next block's first norm output
+
+
 @BLOCKS.register("sandwich")
 class SandwichBlock(Block):
     """Norms before AND after each sublayer: ``x += post_a(mixer(norm_a(x)))``, then, if the layer has a
     feed-forward, ``x += post_b(feed_forward(norm_b(x)))``.  A sublayer writes its result to a 32-bit buffer
     of the residual stream's shape (parts with ``can_overwrite`` write it, for others the buffer is zeroed and
     they add); the norm on the output adds it to the stream (``Norm.add_normed``) and, where it can, makes
-    the next sublayer's input in the same pass."""
+    the next sublayer's input in the same pass: the feed-forward's inside the layer, and across the seam the
+    next layer's first norm when that layer is of this kind too (``fold_request`` / ``prepare_next``)."""
 
     ROLES = {"mixer_norm": NORMS, "mixer": MIXERS, "mixer_post_norm": NORMS, "feed_forward_norm": NORMS,
              "feed_forward": FEED_FORWARDS, "feed_forward_post_norm": NORMS}
     OPTIONAL = ("feed_forward_norm", "feed_forward", "feed_forward_post_norm")
+    folds_norms = True
 
     def __init__(self, layer_spec, ctx):
         super().__init__(layer_spec, ctx)
@@ -184,7 +195,7 @@ class SandwichBlock(Block):
         self.ff_norm, self.ff, self.ff_post = p.get("feed_forward_norm"), p.get("feed_forward"), p.get("feed_forward_post_norm")
         if len({self.ff_norm is None, self.ff is None, self.ff_post is None}) != 1:
             raise ValueError(f"layer {layer_spec.prefix!r}: a feed-forward and its two norms come together")
-        self.fuse_norms = True              # tests switch it off to run the two norms between the sublayers one by one
+        self.fuse_norms = True              # tests switch it off to run every norm as a kernel of its own
 
     @staticmethod
     def _run(part, y, args):
@@ -194,19 +205,29 @@ class SandwichBlock(Block):
             y.zero_()
             part.forward(*args)
 
-    def forward(self, x, step, cache, state, append: bool):
+    def _h(self, step, size: int):
+        return self.ctx.workspace.buffer("block.h", (self.ctx.max_step_tokens, size), self.ctx.dtype)[:step.num_tokens]
+
+    def fold_request(self, step):
+        size = getattr(self.mixer_norm, "size", None)
+        if not self.fuse_norms or size is None:
+            return None
+        request = self.mixer_norm.fold_request(self._h(step, size))
+        return NormAhead(request) if request is not None else None
+
+    def forward(self, x, step, cache, state, append: bool, prepared=None, prepare_next=None):
         ws, cap, T = self.ctx.workspace, self.ctx.max_step_tokens, step.num_tokens
-        h = ws.buffer("block.h", (cap, x.shape[1]), self.ctx.dtype)[:T]
+        h = self._h(step, x.shape[1])
         y = ws.buffer("block.branch", (cap, x.shape[1]), torch.float32)[:T]
-        self.mixer_norm.forward(x, h)
+        ahead = prepare_next if (self.fuse_norms and isinstance(prepare_next, NormAhead)) else None
+        if prepared is not NORMED:
+            self.mixer_norm.forward(x, h)
         self._run(self.mixer, y, (h, y, step, cache, state, append))
         if self.ff is None:
-            self.mixer_post.add_normed(y, x)
-            return None
+            return NORMED if self.mixer_post.add_normed(y, x, then=ahead) else None
         if not (self.fuse_norms and self.mixer_post.add_normed(y, x, then=self.ff_norm, then_out=h)):
             if not self.fuse_norms:
                 self.mixer_post.add_normed(y, x)
             self.ff_norm.forward(x, h)
         self._run(self.ff, y, (h, y, step))
-        self.ff_post.add_normed(y, x)
-        return None
+        return NORMED if self.ff_post.add_normed(y, x, then=ahead) else None

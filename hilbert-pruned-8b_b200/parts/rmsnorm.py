@@ -42,9 +42,13 @@ class RMSNorm(Norm):
         return (self.weight, self.offset, self.eps, out)
 
     def add_normed(self, y, x, then=None, then_out=None) -> bool:
-        """``x += norm(y)``; with ``then`` (the norm that reads ``x`` next, if it is an RMSNorm too) also
-        ``then_out = then(x)`` in the same pass.  Returns whether ``then_out`` was written."""
-        fuse = isinstance(then, RMSNorm) and then_out is not None and then.size == self.size
-        self.ctx.ops.rmsnorm_add(y, self.weight, self.eps, self.offset, x, (then.weight, then.eps, then.offset) if fuse else None,
-                                 then_out if fuse else None)
-        return fuse
+        """``x += norm(y)``; with ``then`` (the RMS norm that reads ``x`` next, or what its ``fold_request`` returned:
+        ``(weight, offset, eps, out)``) also ``then(x)`` in the same pass, into ``then_out`` or the request's buffer.
+        Returns whether that output was written."""
+        second = out2 = None
+        if isinstance(then, RMSNorm) and then_out is not None and then.size == self.size:
+            second, out2 = (then.weight, then.eps, then.offset), then_out
+        elif isinstance(then, tuple) and len(then) == 4 and tuple(then[3].shape) == tuple(x.shape):
+            second, out2 = (then[0], then[2], then[1]), then[3]
+        self.ctx.ops.rmsnorm_add(y, self.weight, self.eps, self.offset, x, second, out2)
+        return second is not None
